@@ -32,11 +32,19 @@ class NormSpec:
 class PositionSpec:
     """How positions enter a mixer.  ``kind`` "rope_neox": rotate the pairs
     (i, i + rotary_dim/2) of the first ``rotary_dim`` lanes of a head by
-    position * theta^(-2i/rotary_dim)."""
+    position * theta^(-2i/rotary_dim).  ``kind`` "rope_pairs": the same angles on the pairs (2i, 2i + 1)."""
     kind: str
     theta: float
     rotary_dim: int
     position_scale: float = 1.0
+    # Frequencies rescaled between two wavelengths (``scaling_factor`` > 0): with n(t) = rotary_dim * ln(original /
+    # (2 pi t)) / (2 ln theta), lo = max(floor(n(fast)), 0), hi = min(ceil(n(slow)), rotary_dim - 1) and
+    # ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), pair i turns at f_i / factor * ramp_i + f_i * (1 - ramp_i),
+    # and cos and sin are multiplied by 0.1 * ln(factor) + 1.
+    scaling_factor: float = 0.0
+    scaling_original: float = 0.0
+    scaling_fast: float = 0.0
+    scaling_slow: float = 0.0
 
 
 @dataclass(frozen=True)
@@ -67,14 +75,27 @@ class AttentionSpec(MixerSpec):
     tensor_names: str = "proj"       # "proj": <name>.q_proj.weight / .bias ...; "short": <name>.q, <name>.q.b, ... <name>.o
     chunk: int = 0                   # n: positions are cut into blocks of n from position 0 of the sequence, and a
                                      # query sees the keys of its own block up to itself (not together with window)
+    out_bias: bool = False           # the output projection has a bias (required, unlike out_bias_optional)
+    values_are_keys: bool = False    # no value projection: a position's value is its key as projected, before the
+                                     # per-head norm and the rotation
+    sink: bool = False               # a learned logit per head ("<name>.sink") whose exponential joins the softmax's
+                                     # denominator: it has no key and no value, is not scaled, and counts once
+    out_gate: bool = False           # the concatenated heads are multiplied, lane by lane, by sigmoid(W_g h)
+                                     # ("<name>.g", n_heads * v_head_dim rows) before the output projection
 
 
 @dataclass(frozen=True)
 class LatentAttentionSpec(MixerSpec):
     """Attention whose keys and values are products of one latent vector per position: c = rmsnorm(W_dkv h) of
     ``latent_dim`` lanes is all that is kept; head a has k = W_uk[a] c (``head_dim`` lanes) and v = W_uv[a] c
-    (``v_head_dim`` lanes).  No positions enter; causal; scores times ``scale``.  With ``head_gate`` every head's
-    output is multiplied by the sigmoid of one more projection of h (one logit per head)."""
+    (``v_head_dim`` lanes).  Causal; scores times ``scale``.  With ``head_gate`` every head's
+    output is multiplied by the sigmoid of one more projection of h (one logit per head).
+
+    ``rot_dim`` R > 0: a head's query has R more lanes after its ``head_dim`` unrotated ones, W_dkv has R more rows
+    after the latent's (not normed), and those R lanes, rotated by ``position``, are one key part that all heads
+    share: score = (q_unrotated . k_unrotated + q_rotated . k_rotated) * scale; the latent and the rotated key part
+    are what is kept.  ``q_rank`` > 0: queries go through a latent of their own, q = W_uq rmsnorm(W_dq h).
+    ``sink``: as in ``AttentionSpec``.  A layer that reads another layer's cache has no W_dkv."""
     hidden_size: int = 0
     n_heads: int = 0
     head_dim: int = 0
@@ -83,6 +104,28 @@ class LatentAttentionSpec(MixerSpec):
     scale: float = 0.0
     eps: float = 1e-6
     head_gate: bool = False
+    rot_dim: int = 0
+    position: Optional[PositionSpec] = None
+    q_rank: int = 0
+    sink: bool = False
+
+
+@dataclass(frozen=True)
+class GatedDeltaSpec(MixerSpec):
+    """The gated delta rule, a recurrent mixer: per head a state S of ``key_dim`` x ``value_dim`` 32-bit numbers.
+    q and k have ``n_kv_heads`` heads (head h of ``n_heads`` uses q/k head h // (n_heads / n_kv_heads)), v has
+    ``n_heads``; each passes a causal convolution of ``conv`` taps per channel and SiLU; q and k become unit vectors
+    (x / sqrt(sum x^2 + 1e-6); q also times key_dim^-1/2).  Per token and head: beta = sigmoid(W_b h),
+    g = exp(-exp(A_log) softplus(W_a h + dt_bias)); S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q.
+    The heads' outputs are RMS-normed (``eps``, one weight of ``value_dim`` lanes), gated by silu(W_g h) and projected
+    back.  The last ``conv`` - 1 inputs of the convolutions are state too."""
+    hidden_size: int = 0
+    n_heads: int = 0
+    n_kv_heads: int = 0
+    key_dim: int = 0
+    value_dim: int = 0
+    conv: int = 0
+    eps: float = 1e-6
 
 
 @dataclass(frozen=True)
@@ -146,7 +189,8 @@ class BlockSpec:
     x += mixer(norm1(x)); x += feed_forward(norm2(x)).  ``kind`` "sandwich" norms each sublayer's output too:
     x += norm1_post(mixer(norm1(x))); x += norm2_post(feed_forward(norm2(x))), and a layer without a
     feed-forward (``feed_forward`` None) has the first sublayer only.  ``kind`` "parallel": both sublayers read the
-    stream as it enters the layer, x += mixer(norm1(x)) + feed_forward(norm2(x)); without a feed-forward norm2 is not used (its tensor is optional)."""
+    stream as it enters the layer, x += mixer(norm1(x)) + feed_forward(norm2(x)); without a feed-forward norm2 is not used (its tensor is optional);
+    a "parallel" layer with a feed-forward and ``norm2`` None has one norm, whose output both sublayers read."""
     kind: str
     norm1: NormSpec
     mixer: MixerSpec

@@ -332,29 +332,30 @@ extern "C" int nncpu_linear_simt(const void* A, int a_dt, const void* W, int w_d
 }
 
 // ---------------------------------------------------------------------------
-// Rotation table of a step: cs[t, i] = (cos, sin)(float(pos_t) * pos_scale * inv_freq[i]), or with
+// Rotation table of a step: cs[t, i] = stretch * (cos, sin)(float(pos_t) * pos_scale * inv_freq[i]), or with
 // by_pair the same values laid out [i, t] for readers whose lanes are tokens.
 // Computed once per step and read by every layer that shares the encoding.
 // ---------------------------------------------------------------------------
 __global__ void rope_table_kernel(const int* __restrict__ pos, const float* __restrict__ inv_freq,
-                                  float2* __restrict__ cs, int n_tok, int half, float pos_scale, int by_pair) {
+                                  float2* __restrict__ cs, int n_tok, int half, float pos_scale, int by_pair,
+                                  float stretch) {
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= n_tok * half) return;
     const int t = by_pair ? idx % n_tok : idx / half, i = by_pair ? idx / n_tok : idx % half;
     const float theta = ((float)pos[t] * pos_scale) * inv_freq[i];
     float s, c;
     sincosf(theta, &s, &c);
-    cs[idx] = make_float2(c, s);
+    cs[idx] = stretch == 1.0f ? make_float2(c, s) : make_float2(c * stretch, s * stretch);
 }
 
 extern "C" int nncpu_rope_table(const int* pos, const float* inv_freq, float* cs, int n_tok, int half,
-                                float pos_scale, int by_pair, void* stream) {
+                                float pos_scale, int by_pair, float stretch, void* stream) {
     NN_CHECK(n_tok >= 0 && half > 0, "rope_table: %d tokens, %d pairs", n_tok, half);
     if (n_tok == 0) return 0;
     const int total = n_tok * half;
     NN_CHECK((uintptr_t)cs % 8 == 0, "rope_table: the table must be 8-byte aligned (it is written as cos/sin pairs)");
     rope_table_kernel<<<(total + 255) / 256, 256, 0, (cudaStream_t)stream>>>(pos, inv_freq, (float2*)cs, n_tok,
-                                                                             half, pos_scale, by_pair);
+                                                                             half, pos_scale, by_pair, stretch);
     NN_LAUNCH_OK("rope_table");
     return 0;
 }
@@ -367,6 +368,9 @@ extern "C" int nncpu_rope_table(const int* pos, const float* inv_freq, float* cs
 // rows.  With n_kv == 0 the mixer reads another layer's cache and only q is
 // processed.  A query temperature (temp_coef != 0) multiplies the query at
 // position p by 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1).
+// With v_from_k the rows hold no v heads: a value head is the key head of the
+// same number as projected (raw), and vd == hd.  A row is ld elements long
+// (it may hold more than the heads: a gate's logits after them).
 // ---------------------------------------------------------------------------
 __global__ void qk_norm_rope_append_kernel(const void* __restrict__ qkv, int in_dt, const void* __restrict__ q_gamma,
                                            const void* __restrict__ k_gamma, int g_dt, float eps,
@@ -375,7 +379,7 @@ __global__ void qk_norm_rope_append_kernel(const void* __restrict__ qkv, int in_
                                            const int* __restrict__ block_table, int bt_stride,
                                            void* __restrict__ k_pages, void* __restrict__ v_pages, int kv_dt,
                                            void* __restrict__ q_out, int q_dt, int n_tok, int n_heads, int n_kv,
-                                           int hd, int vd, float temp_coef, int temp_every) {
+                                           int hd, int vd, float temp_coef, int temp_every, int ld, int v_from_k) {
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int per_tok = n_heads + 2 * n_kv;
@@ -385,9 +389,10 @@ __global__ void qk_norm_rope_append_kernel(const void* __restrict__ qkv, int in_
     const int seq = tok_seq[t];
     const bool is_q = h < n_heads, is_k = !is_q && h < n_heads + n_kv;
     const int len = (is_q || is_k) ? hd : vd;
-    const size_t row = (size_t)(n_heads + n_kv) * hd + (size_t)n_kv * vd;
+    const size_t row = (size_t)ld;
     float* x = smem + warp * max(hd, vd);
     const size_t in_base = (size_t)t * row + ((is_q || is_k) ? (size_t)h * hd
+                                                              : v_from_k ? (size_t)(h - n_kv) * hd
                                                               : (size_t)(n_heads + n_kv) * hd + (size_t)(h - n_heads - n_kv) * vd);
     const void* gamma = is_q ? q_gamma : (is_k ? k_gamma : nullptr);
 
@@ -439,7 +444,7 @@ qk_norm_rope_append_fast_kernel(const float* __restrict__ qkv, const void* __res
                                 const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                                 const int* __restrict__ block_table, int bt_stride, __nv_bfloat16* __restrict__ k_pages,
                                 __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ q_out, int n_tok,
-                                int n_heads, int n_kv, float temp_coef, int temp_every) {
+                                int n_heads, int n_kv, float temp_coef, int temp_every, int ld, int v_from_k) {
     constexpr int hd = 32 * EPL, half = hd / 2;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int per_tok = n_heads + 2 * n_kv;
@@ -447,7 +452,7 @@ qk_norm_rope_append_fast_kernel(const float* __restrict__ qkv, const void* __res
     if (item >= (long)n_tok * per_tok) return;
     const int t = (int)(item / per_tok), h = (int)(item % per_tok);
     const bool is_q = h < n_heads, is_k = !is_q && h < n_heads + n_kv;
-    const float* src = qkv + ((size_t)t * per_tok + h) * hd + lane * EPL;
+    const float* src = qkv + (size_t)t * ld + (size_t)((!is_q && !is_k && v_from_k) ? h - n_kv : h) * hd + lane * EPL;
     float x[EPL];
     if (EPL == 4) {
         const float4 v = *reinterpret_cast<const float4*>(src);
@@ -504,8 +509,11 @@ extern "C" int nncpu_qk_norm_rope_append(const void* qkv, int in_dt, const void*
                                          int g_dt, float eps, const float* cs, int rot_half, const int* tok_seq,
                                          const int* tok_pos, const int* block_table, int bt_stride, void* k_pages,
                                          void* v_pages, int kv_dt, void* q_out, int q_dt, int n_tok, int n_heads,
-                                         int n_kv, int hd, int vd, float temp_coef, int temp_every, void* stream) {
+                                         int n_kv, int hd, int vd, float temp_coef, int temp_every, int ld, int v_from_k,
+                                         void* stream) {
     NN_CHECK(n_tok >= 0 && n_heads > 0 && n_kv >= 0 && hd > 0 && vd > 0, "qk_norm_rope_append: sizes");
+    NN_CHECK(!v_from_k || vd == hd, "qk_norm_rope_append: values that are the keys have the keys' size, not %d", vd);
+    NN_CHECK(ld >= (n_heads + n_kv) * hd + (v_from_k ? 0 : n_kv * vd), "qk_norm_rope_append: rows of %d elements", ld);
     NN_CHECK(vd <= 1024, "qk_norm_rope_append: value size %d is above 1024", vd);
     NN_CHECK(temp_coef == 0.0f || temp_every > 0, "qk_norm_rope_append: a query temperature every %d positions", temp_every);
     NN_CHECK((cs == nullptr || hd % 2 == 0) && 2 * rot_half <= hd, "qk_norm_rope_append: head size %d with %d rotated pairs", hd,
@@ -514,19 +522,19 @@ extern "C" int nncpu_qk_norm_rope_append(const void* qkv, int in_dt, const void*
     NN_CHECK(hd <= 1024, "qk_norm_rope_append: head size %d is above 1024", hd);
     if (n_tok == 0) return 0;
     if (in_dt == DT_F32 && q_dt == DT_BF16 && (n_kv == 0 || kv_dt == DT_BF16) && (hd == 64 || hd == 128) && vd == hd &&
-        (cs == nullptr || 2 * rot_half == hd) && (uintptr_t)qkv % 16 == 0 && (uintptr_t)q_out % 16 == 0) {
+        (cs == nullptr || 2 * rot_half == hd) && (uintptr_t)qkv % 16 == 0 && (uintptr_t)q_out % 16 == 0 && ld % 4 == 0) {
         const long n_items = (long)n_tok * (n_heads + 2 * n_kv);
         const unsigned n_blocks = (unsigned)((n_items + 7) / 8);
         if (hd == 128)
             qk_norm_rope_append_fast_kernel<4><<<n_blocks, 256, 0, (cudaStream_t)stream>>>(
                 (const float*)qkv, q_gamma, k_gamma, g_dt, eps, (const float2*)cs, tok_seq, tok_pos, block_table,
                 bt_stride, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, (__nv_bfloat16*)q_out, n_tok, n_heads, n_kv,
-                temp_coef, temp_every);
+                temp_coef, temp_every, ld, v_from_k);
         else
             qk_norm_rope_append_fast_kernel<2><<<n_blocks, 256, 0, (cudaStream_t)stream>>>(
                 (const float*)qkv, q_gamma, k_gamma, g_dt, eps, (const float2*)cs, tok_seq, tok_pos, block_table,
                 bt_stride, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, (__nv_bfloat16*)q_out, n_tok, n_heads, n_kv,
-                temp_coef, temp_every);
+                temp_coef, temp_every, ld, v_from_k);
         NN_LAUNCH_OK("qk_norm_rope_append");
         return 0;
     }
@@ -536,7 +544,7 @@ extern "C" int nncpu_qk_norm_rope_append(const void* qkv, int in_dt, const void*
     qk_norm_rope_append_kernel<<<(unsigned)blocks, warps * 32, warps * (hd > vd ? hd : vd) * sizeof(float),
                                  (cudaStream_t)stream>>>(
         qkv, in_dt, q_gamma, k_gamma, g_dt, eps, (const float2*)cs, rot_half, tok_seq, tok_pos, block_table,
-        bt_stride, k_pages, v_pages, kv_dt, q_out, q_dt, n_tok, n_heads, n_kv, hd, vd, temp_coef, temp_every);
+        bt_stride, k_pages, v_pages, kv_dt, q_out, q_dt, n_tok, n_heads, n_kv, hd, vd, temp_coef, temp_every, ld, v_from_k);
     NN_LAUNCH_OK("qk_norm_rope_append");
     return 0;
 }
@@ -550,6 +558,8 @@ extern "C" int nncpu_qk_norm_rope_append(const void* qkv, int in_dt, const void*
 // result does not depend on the batch or on how tokens were cut into steps.
 // Values have vd lanes a head (the output too).  With slope_base != 0 head h
 // takes slope_h * (pos - key) off its scaled scores, slope_h = 2^(-slope_base (h + 1) / n_heads).
+// With sinks (float32 [n_heads]) the softmax's denominator of head h also holds exp(sinks[h]): a term without
+// key or value, not scaled, counted once.
 // ---------------------------------------------------------------------------
 constexpr int kAttnThreads = 128;
 
@@ -557,7 +567,8 @@ __global__ void __launch_bounds__(kAttnThreads)
 attention_kernel(const void* __restrict__ q, int q_dt, const void* __restrict__ k_pages,
                  const void* __restrict__ v_pages, int kv_dt, const int* __restrict__ block_table, int bt_stride,
                  const int* __restrict__ tok_seq, const int* __restrict__ tok_pos, void* __restrict__ out,
-                 int out_dt, int n_heads, int n_kv, int hd, int vd, float scale, int window, float slope_base) {
+                 int out_dt, int n_heads, int n_kv, int hd, int vd, float scale, int window, float slope_base,
+                 const float* __restrict__ sinks) {
     extern __shared__ float smem[];
     float* qs = smem;                       // hd
     float* p = smem + hd;                   // kAttnThreads
@@ -615,6 +626,7 @@ attention_kernel(const void* __restrict__ q, int q_dt, const void* __restrict__ 
         }
         __syncthreads();
     }
+    if (sinks != nullptr) l += expf(sinks[h] - m);      // the maximum is that of the keys: a query sees itself at least
     const float inv = l > 0.0f ? 1.0f / l : 0.0f;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -626,7 +638,7 @@ attention_kernel(const void* __restrict__ q, int q_dt, const void* __restrict__ 
 extern "C" int nncpu_attention(const void* q, int q_dt, const void* k_pages, const void* v_pages, int kv_dt,
                                const int* block_table, int bt_stride, const int* tok_seq, const int* tok_pos,
                                void* out, int out_dt, int n_tok, int n_heads, int n_kv, int hd, int vd, float scale,
-                               int window, float slope_base, void* stream) {
+                               int window, float slope_base, const float* sinks, void* stream) {
     NN_CHECK(n_tok >= 0 && n_heads > 0 && n_kv > 0 && n_heads % n_kv == 0,
              "attention: %d heads over %d key/value heads", n_heads, n_kv);
     NN_CHECK(hd > 0 && hd <= 1024, "attention: head size %d must be positive and at most 1024", hd);
@@ -637,7 +649,7 @@ extern "C" int nncpu_attention(const void* q, int q_dt, const void* k_pages, con
     attention_kernel<<<grid, kAttnThreads, smem, (cudaStream_t)stream>>>(q, q_dt, k_pages, v_pages, kv_dt,
                                                                          block_table, bt_stride, tok_seq, tok_pos,
                                                                          out, out_dt, n_heads, n_kv, hd, vd, scale,
-                                                                         window, slope_base);
+                                                                         window, slope_base, sinks);
     NN_LAUNCH_OK("attention");
     return 0;
 }
@@ -1730,23 +1742,39 @@ extern "C" int nncpu_linear_heads(const void* A, int a_dt, const void* W, int w_
 
 // ---------------------------------------------------------------------------
 // Latent attention keeps one vector per position: c = rmsnorm(z) * gamma of `rank` lanes, where z sits at column
-// `col` of the rows of proj [n_tok, ld] (32-bit).  It goes to the token's row of the key pages (one key/value head
-// of `rank` lanes); the same pages serve as values.  One block per token.  With q_out (bfloat16 [n_tok, q_size]) the
+// `col` of the rows of proj [n_tok, ld] (32-bit).  It goes to the token's row of the key pages (one key/value head);
+// the same pages serve as values.  One block per token.  With q_out (bfloat16 [n_tok, q_size]) the
 // first q_size columns of the token's row (the queries) are copied there rounded to bfloat16, for the per-head
 // products on the tensor cores.
+// With rot_dim > 0 the row of proj holds rot_dim more lanes right after z: a key part that all heads share.  Its first
+// 2 * rot_half lanes are rotated in neighbouring pairs (2i, 2i + 1) by cs[t, i] = (cos, sin), the rest pass, and the
+// part follows c in the page row, which is rank + rot_dim lanes long.  With pages null the layer reads another layer's
+// cache and nothing is appended.
+// With qn_gamma the queries' own latent is normed too: cq_out[t] = rmsnorm(proj[t, qn_col : qn_col + qn_rank]) * qn_gamma.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(128)
 latent_append_kernel(const float* __restrict__ proj, int ld, int col, const void* __restrict__ gamma, int g_dt,
                      float eps, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                      const int* __restrict__ block_table, int bt_stride, void* __restrict__ pages, int kv_dt,
-                     int rank, __nv_bfloat16* __restrict__ q_out, int q_size) {
+                     int rank, __nv_bfloat16* __restrict__ q_out, int q_size, int rot_dim,
+                     const float2* __restrict__ cs, int rot_half, const void* __restrict__ qn_gamma, int qn_col,
+                     int qn_rank, void* __restrict__ cq_out, int cq_dt) {
     __shared__ float scratch[33];
     const int t = blockIdx.x;
     if (q_out != nullptr)
         for (int i = threadIdx.x; i < q_size; i += blockDim.x)
             q_out[(size_t)t * q_size + i] = __float2bfloat16_rn(proj[(size_t)t * ld + i]);
+    if (qn_gamma != nullptr) {
+        const float* zq = proj + (size_t)t * ld + qn_col;
+        float sq = 0.0f;
+        for (int i = threadIdx.x; i < qn_rank; i += blockDim.x) sq = fmaf(zq[i], zq[i], sq);
+        sq = block_sum(sq, scratch);
+        const float sc = 1.0f / sqrtf(sq * (1.0f / (float)qn_rank) + eps);
+        for (int i = threadIdx.x; i < qn_rank; i += blockDim.x)
+            st_f(cq_out, (size_t)t * qn_rank + i, cq_dt, (zq[i] * sc) * ld_f(qn_gamma, i, g_dt));
+    }
     const int seq = tok_seq[t];
-    if (seq < 0) return;                    // a padded row owns no place in the cache
+    if (seq < 0 || pages == nullptr) return;   // a padded row owns no place in the cache
     const float* z = proj + (size_t)t * ld + col;
     float ss = 0.0f;
     for (int i = threadIdx.x; i < rank; i += blockDim.x) ss = fmaf(z[i], z[i], ss);
@@ -1755,21 +1783,103 @@ latent_append_kernel(const float* __restrict__ proj, int ld, int col, const void
     const int pos = tok_pos[t];
     const int page = block_table[(size_t)seq * bt_stride + pos / kPage];
     if (page < 0) return;
-    const size_t o = ((size_t)page * kPage + pos % kPage) * rank;
+    const size_t o = ((size_t)page * kPage + pos % kPage) * (size_t)(rank + rot_dim);
     for (int i = threadIdx.x; i < rank; i += blockDim.x) st_f(pages, o + i, kv_dt, (z[i] * scale) * ld_f(gamma, i, g_dt));
+    const float* zr = z + rank;
+    for (int i = threadIdx.x; i < rot_half; i += blockDim.x) {
+        const float2 c = cs[(size_t)t * rot_half + i];
+        const float u = zr[2 * i], v = zr[2 * i + 1];
+        st_f(pages, o + rank + 2 * i, kv_dt, c.x * u - c.y * v);
+        st_f(pages, o + rank + 2 * i + 1, kv_dt, c.x * v + c.y * u);
+    }
+    for (int i = 2 * rot_half + threadIdx.x; i < rot_dim; i += blockDim.x) st_f(pages, o + rank + i, kv_dt, zr[i]);
 }
 
 extern "C" int nncpu_latent_append(const float* proj, int ld, int col, const void* gamma, int g_dt, float eps,
                                    const int* tok_seq, const int* tok_pos, const int* block_table, int bt_stride,
-                                   void* pages, int kv_dt, int n_tok, int rank, void* q_out, int q_size, void* stream) {
-    NN_CHECK(n_tok >= 0 && rank > 0 && col >= 0 && ld >= col + rank, "latent append: %d tokens, rank %d at column %d of %d",
-             n_tok, rank, col, ld);
+                                   void* pages, int kv_dt, int n_tok, int rank, void* q_out, int q_size, int rot_dim,
+                                   const float* cs, int rot_half, const void* qn_gamma, int qn_col, int qn_rank,
+                                   void* cq_out, int cq_dt, void* stream) {
+    NN_CHECK(n_tok >= 0 && rank > 0 && col >= 0 && rot_dim >= 0 && (pages == nullptr || ld >= col + rank + rot_dim),
+             "latent append: %d tokens, rank %d + %d at column %d of %d", n_tok, rank, rot_dim, col, ld);
     NN_CHECK(q_out == nullptr || (q_size > 0 && q_size <= ld), "latent append: %d query lanes of a row of %d", q_size, ld);
+    NN_CHECK(rot_half >= 0 && 2 * rot_half <= rot_dim && (rot_half == 0 || cs != nullptr) && (uintptr_t)cs % 8 == 0,
+             "latent append: %d rotated pairs of %d lanes", rot_half, rot_dim);
+    NN_CHECK(qn_gamma == nullptr || (qn_rank > 0 && qn_col >= 0 && qn_col + qn_rank <= ld && cq_out != nullptr),
+             "latent append: a query latent of %d lanes at column %d of %d", qn_rank, qn_col, ld);
     if (n_tok == 0) return 0;
     latent_append_kernel<<<n_tok, 128, 0, (cudaStream_t)stream>>>(proj, ld, col, gamma, g_dt, eps, tok_seq, tok_pos,
                                                                   block_table, bt_stride, pages, kv_dt, rank,
-                                                                  (__nv_bfloat16*)q_out, q_size);
+                                                                  (__nv_bfloat16*)q_out, q_size, rot_dim,
+                                                                  (const float2*)cs, rot_half, qn_gamma, qn_col, qn_rank,
+                                                                  cq_out, cq_dt);
     NN_LAUNCH_OK("latent append");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// The queries of latent attention with a rotated part: q [n_tok, n_heads * (hd + rot_dim)] (32-bit) holds, head by
+// head, hd unrotated lanes and then rot_dim lanes of which the first 2 * rot_half are rotated in neighbouring pairs
+// by cs[t, i].  The rotated part goes to q_lat[t, head, rank : rank + rot_dim] (rows of n_heads * (rank + rot_dim)
+// lanes; the first `rank` lanes of a head are the per-head product's to fill).  With q16 the whole row of q is also
+// left there rounded to bfloat16, for that product on the tensor cores.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(128)
+latent_query_kernel(const float* __restrict__ q, int n_heads, int hd, int rot_dim, const float2* __restrict__ cs,
+                    int rot_half, void* __restrict__ q_lat, int lat_dt, int rank, __nv_bfloat16* __restrict__ q16) {
+    const int t = blockIdx.x;
+    const int per = hd + rot_dim;
+    const float* row = q + (size_t)t * n_heads * per;
+    if (q16 != nullptr)
+        for (int i = threadIdx.x; i < n_heads * per; i += blockDim.x)
+            q16[(size_t)t * n_heads * per + i] = __float2bfloat16_rn(row[i]);
+    const size_t o = (size_t)t * n_heads * (rank + rot_dim);
+    for (int idx = threadIdx.x; idx < n_heads * rot_half; idx += blockDim.x) {
+        const int a = idx / rot_half, i = idx % rot_half;
+        const float2 c = cs[(size_t)t * rot_half + i];
+        const float u = row[a * per + hd + 2 * i], v = row[a * per + hd + 2 * i + 1];
+        st_f(q_lat, o + (size_t)a * (rank + rot_dim) + rank + 2 * i, lat_dt, c.x * u - c.y * v);
+        st_f(q_lat, o + (size_t)a * (rank + rot_dim) + rank + 2 * i + 1, lat_dt, c.x * v + c.y * u);
+    }
+    const int rest = rot_dim - 2 * rot_half;
+    for (int idx = threadIdx.x; idx < n_heads * rest; idx += blockDim.x) {
+        const int a = idx / rest, i = 2 * rot_half + idx % rest;
+        st_f(q_lat, o + (size_t)a * (rank + rot_dim) + rank + i, lat_dt, row[a * per + hd + i]);
+    }
+}
+
+extern "C" int nncpu_latent_query(const float* q, int n_tok, int n_heads, int hd, int rot_dim, const float* cs,
+                                  int rot_half, void* q_lat, int lat_dt, int rank, void* q16, void* stream) {
+    NN_CHECK(n_tok >= 0 && n_heads > 0 && hd > 0 && rot_dim >= 0 && rank > 0, "latent query: sizes");
+    NN_CHECK(rot_half >= 0 && 2 * rot_half <= rot_dim && (rot_half == 0 || cs != nullptr) && (uintptr_t)cs % 8 == 0,
+             "latent query: %d rotated pairs of %d lanes", rot_half, rot_dim);
+    if (n_tok == 0) return 0;
+    latent_query_kernel<<<n_tok, 128, 0, (cudaStream_t)stream>>>(q, n_heads, hd, rot_dim, (const float2*)cs, rot_half,
+                                                                 q_lat, lat_dt, rank, (__nv_bfloat16*)q16);
+    NN_LAUNCH_OK("latent query");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// An elementwise gate: x[t, i] *= sigmoid(g[t, col + i]) for i < width; x in either element type, g 32-bit with
+// rows of ld lanes.  The sigmoid and the product are 32-bit.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+sigmoid_gate_kernel(void* __restrict__ x, int x_dt, const float* __restrict__ g, int ld, int col, long n_tok, int width) {
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n_tok * width) return;
+    const long t = idx / width;
+    const int i = (int)(idx % width);
+    const float z = g[(size_t)t * ld + col + i];
+    st_f(x, idx, x_dt, ld_f(x, idx, x_dt) * (1.0f / (1.0f + expf(0.0f - z))));
+}
+
+extern "C" int nncpu_sigmoid_gate(void* x, int x_dt, const float* g, int ld, int col, int n_tok, int width, void* stream) {
+    NN_CHECK(n_tok >= 0 && width > 0 && col >= 0 && ld >= col + width, "sigmoid gate: %d lanes at column %d of %d", width, col, ld);
+    if (n_tok == 0) return 0;
+    const long total = (long)n_tok * width;
+    sigmoid_gate_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, x_dt, g, ld, col, n_tok, width);
+    NN_LAUNCH_OK("sigmoid gate");
     return 0;
 }
 

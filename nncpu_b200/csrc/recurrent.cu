@@ -359,3 +359,268 @@ extern "C" int nncpu_gla_step(const float* proj, int row, const float* z, float*
     NN_LAUNCH_OK("gla_step");
     return 0;
 }
+
+// ---------------------------------------------------------------------------
+// The gated delta rule.  Per head, with a state S of d rows (key channels) and e columns (value channels), a decay
+// g and a write strength beta per token and head, unit vectors k and q (q also times d^-1/2):
+//     S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
+// q and k have G heads (head h of H uses q/k head h / (H / G)), v has H.  Before that, q, k and v each pass a causal
+// convolution over time per channel (taps weights a channel, the last one the current token's, zeros before the
+// sequence's start) and SiLU.  The last taps - 1 inputs of the convolutions are per-sequence state, like S.
+//
+// The rows of proj [n_tok, ld] (32-bit) hold, in this order: q (G d), k (G d), v (H e), the output gate's logits (H e),
+// the logits of beta (H), the decays' inputs (H).  The first C = 2 G d + H e of them are the convolutions' channels;
+// A slot's state and its convolution inputs may be parts of one row per slot: both are addressed as base + slot *
+// slot_stride floats.  conv_state [taps - 1, C] of a slot holds, for a sequence of n tokens so far, the inputs of positions n - (taps - 1)
+// .. n - 1 (zeros before position 0).
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float softplus_r(float z) { return fmaxf(z, 0.0f) + log1pf(expf(-fabsf(z))); }
+
+constexpr float kUnitEps = 1e-6f;     // inside the root that makes q and k unit vectors
+constexpr int kMaxTaps = 32;
+
+// One warp per (token, item): G query heads, G key heads, H value heads, and one item for the token's H decays and
+// write strengths.  xc [n_tok, C] receives the convolved, activated (and for q, k: normalised) channels, gb [n_tok,
+// 2 H] the decays g and then the strengths beta.  A token of no sequence (tok_seq < 0) gets zeros.
+__global__ void __launch_bounds__(256)
+delta_prepare_kernel(const float* __restrict__ proj, int ld, const void* __restrict__ conv_w, int w_dt,
+                     const float* __restrict__ conv_state, long slot_stride, const int* __restrict__ tok_seq,
+                     const int* __restrict__ seq_slots, const int* __restrict__ cu_seqlens,
+                     const void* __restrict__ a_log, const void* __restrict__ dt_bias, int p_dt,
+                     float* __restrict__ xc, float* __restrict__ gb, long n_items, int H, int G, int d, int e, int taps,
+                     float q_scale) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long item = (long)blockIdx.x * 8 + warp;
+    if (item >= n_items) return;
+    const int per_tok = 2 * G + H + 1;
+    const int t = (int)(item / per_tok), it = (int)(item % per_tok);
+    const int C = 2 * G * d + H * e;
+    const int seq = tok_seq[t];
+    const int slot = seq < 0 ? -1 : seq_slots[seq];
+    if (it == per_tok - 1) {
+        for (int h = lane; h < H; h += 32) {
+            float g = 0.0f, beta = 0.0f;
+            if (slot >= 0) {
+                const float* p = proj + (size_t)t * ld + C + (size_t)H * e;
+                beta = 1.0f / (1.0f + expf(0.0f - p[h]));
+                g = expf(0.0f - expf(ld_f(a_log, h, p_dt)) * softplus_r(p[H + h] + ld_f(dt_bias, h, p_dt)));
+            }
+            gb[(size_t)t * 2 * H + h] = g;
+            gb[(size_t)t * 2 * H + H + h] = beta;
+        }
+        return;
+    }
+    const bool is_v = it >= 2 * G;
+    const int len = is_v ? e : d;
+    const int ch0 = is_v ? 2 * G * d + (it - 2 * G) * e : it * d;
+    float* dst = xc + (size_t)t * C + ch0;
+    if (slot < 0) {
+        for (int i = lane; i < len; i += 32) dst[i] = 0.0f;
+        return;
+    }
+    const int local = t - cu_seqlens[seq];          // the token's place among its sequence's tokens of this step
+    const float* st = conv_state + (size_t)slot * slot_stride;
+    float ss = 0.0f;
+    for (int i = lane; i < len; i += 32) {
+        const int ch = ch0 + i;
+        float acc = 0.0f;
+        for (int j = 0; j < taps; ++j) {
+            const int at = local - (taps - 1) + j;
+            const float x = at >= 0 ? proj[(size_t)(t - local + at) * ld + ch] : st[(size_t)(taps - 1 + at) * C + ch];
+            acc = fmaf(ld_f(conv_w, (size_t)ch * taps + j, w_dt), x, acc);
+        }
+        const float y = acc / (1.0f + expf(0.0f - acc));
+        dst[i] = y;
+        ss = fmaf(y, y, ss);
+    }
+    if (is_v) return;
+    ss = warp_sum(ss);
+    const float scale = (1.0f / sqrtf(ss + kUnitEps)) * (it < G ? q_scale : 1.0f);
+    __syncwarp();
+    for (int i = lane; i < len; i += 32) dst[i] *= scale;      // a lane rereads what it wrote itself
+}
+
+// The convolutions' state after the step: one thread per (sequence, channel) shifts its taps - 1 inputs.
+__global__ void __launch_bounds__(256)
+delta_conv_state_kernel(const float* __restrict__ proj, int ld, float* __restrict__ conv_state, long slot_stride,
+                        const int* __restrict__ seq_slots, const int* __restrict__ cu_seqlens, int n_seqs, int C, int taps) {
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long)n_seqs * C) return;
+    const int seq = (int)(idx / C), ch = (int)(idx % C);
+    const int slot = seq_slots[seq];
+    if (slot < 0) return;
+    const int t0 = cu_seqlens[seq], n = cu_seqlens[seq + 1] - t0;
+    float* st = conv_state + (size_t)slot * slot_stride + ch;
+    float keep[kMaxTaps];
+    for (int s = 0; s < taps - 1; ++s) {
+        const int at = n - (taps - 1) + s;          // the step's token that lands in place s (negative: an older one)
+        keep[s] = at >= 0 ? proj[(size_t)(t0 + at) * ld + ch] : st[(size_t)(taps - 1 + at) * C];
+    }
+    for (int s = 0; s < taps - 1; ++s) st[(size_t)s * C] = keep[s];
+}
+
+extern "C" int nncpu_delta_prepare(const float* proj, int ld, const void* conv_w, int w_dt, float* conv_state,
+                                   long slot_stride, const int* tok_seq, const int* seq_slots, const int* cu_seqlens, const void* a_log,
+                                   const void* dt_bias, int p_dt, float* xc, float* gb, int n_tok, int n_seqs, int H,
+                                   int G, int d, int e, int taps, float q_scale, void* stream) {
+    NN_CHECK(n_tok >= 0 && n_seqs >= 0 && H > 0 && G > 0 && H % G == 0 && d > 0 && e > 0,
+             "delta prepare: %d heads over %d query/key heads of %d x %d", H, G, d, e);
+    NN_CHECK(taps >= 1 && taps <= kMaxTaps, "delta prepare: %d taps (1 to %d)", taps, kMaxTaps);
+    const int C = 2 * G * d + H * e;
+    NN_CHECK(ld >= C + H * e + 2 * H, "delta prepare: rows of %d floats", ld);
+    if (n_tok == 0) return 0;
+    const long n_items = (long)n_tok * (2 * G + H + 1);
+    delta_prepare_kernel<<<(unsigned)((n_items + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
+        proj, ld, conv_w, w_dt, conv_state, slot_stride, tok_seq, seq_slots, cu_seqlens, a_log, dt_bias, p_dt, xc, gb, n_items, H, G, d,
+        e, taps, q_scale);
+    NN_LAUNCH_OK("delta prepare");
+    if (taps > 1 && n_seqs > 0) {
+        const long total = (long)n_seqs * C;
+        delta_conv_state_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+            proj, ld, conv_state, slot_stride, seq_slots, cu_seqlens, n_seqs, C, taps);
+        NN_LAUNCH_OK("delta conv state");
+    }
+    return 0;
+}
+
+__device__ __forceinline__ void cp_async4(void* dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit_() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_one_() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+
+// The recurrence over the step's tokens, sequence by sequence in order.  The columns of S do not depend on one
+// another.  A block of four warps owns 4 * 32 / R columns of one head's state for one sequence; R lanes share a column,
+// lane r of them keeping the rows r + R ii (ii < DR) in registers, so that S^T k costs DR multiply-adds and log2(R)
+// shuffles a token, the only exchange on the chain from token to token (the sum for o is off that chain).  k, q, v,
+// g and beta of a group of tokens are staged in shared memory by asynchronous copies, the next group's in flight under
+// this group's arithmetic.  The order of operations of a (sequence, head, column) does not depend on how the sequence
+// was cut into steps or on what else the step holds.  A negative slot (padding): zeros out, no state touched.
+template <int DR, int R>
+__global__ void __launch_bounds__(128)
+delta_scan_kernel(const float* __restrict__ xc, const float* __restrict__ gb, float* __restrict__ state,
+                  long slot_stride, const int* __restrict__ seq_slots, const int* __restrict__ cu_seqlens, float* __restrict__ o, int H,
+                  int G, int d, int e) {
+    constexpr int DP = DR * R;                      // rows the lanes cover (>= d; the rest hold zeros)
+    constexpr int CW = 32 / R;                      // columns a warp
+    constexpr int COLS = 4 * CW;                    // columns a block
+    constexpr int TB = DP <= 256 ? 8 : (DP <= 512 ? 4 : 2);       // tokens a group
+    constexpr int BUF = TB * (2 * DP + COLS + 2);   // floats a buffer: k, q [TB][DP], v [TB][COLS], (g, beta) [TB]
+    extern __shared__ float dsm_[];
+    const int seq = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int warp = tid >> 5, lane = tid & 31, r = lane % R;
+    const int col_local = warp * CW + lane / R, col0 = blockIdx.z * COLS, col = col0 + col_local;
+    const int t0 = cu_seqlens[seq], t1 = cu_seqlens[seq + 1];
+    const int slot = seq_slots[seq];
+    const int C = 2 * G * d + H * e;
+    if (slot < 0) {
+        if (r == 0 && col < e)
+            for (int t = t0; t < t1; ++t) o[(size_t)t * H * e + (size_t)h * e + col] = 0.0f;
+        return;
+    }
+    const int kvh = h / (H / G);
+    const size_t q_at = (size_t)kvh * d, k_at = (size_t)G * d + (size_t)kvh * d, v_at = 2 * (size_t)G * d + (size_t)h * e;
+    float* s_head = state + (size_t)slot * slot_stride + (size_t)h * d * e;
+    float S[DR];
+#pragma unroll
+    for (int ii = 0; ii < DR; ++ii) {
+        const int i = r + R * ii;
+        S[ii] = (i < d && col < e) ? s_head[(size_t)i * e + col] : 0.0f;
+    }
+    for (int i = tid; i < 2 * BUF; i += 128) dsm_[i] = 0.0f;      // rows beyond d and columns beyond e stay zero
+    __syncthreads();
+    auto stage = [&](int g0, int buf) {
+        const int nt = min(TB, t1 - g0);
+        float* kb = dsm_ + buf * BUF;
+        float* qb = kb + TB * DP;
+        float* vb = qb + TB * DP;
+        float* gbb = vb + TB * COLS;
+        for (int idx = tid; idx < nt * d; idx += 128) {
+            const int tt = idx / d, i = idx % d;
+            const float* src = xc + (size_t)(g0 + tt) * C;
+            cp_async4(kb + tt * DP + i, src + k_at + i);
+            cp_async4(qb + tt * DP + i, src + q_at + i);
+        }
+        for (int idx = tid; idx < nt * COLS; idx += 128) {
+            const int tt = idx / COLS, c = idx % COLS;
+            if (col0 + c < e) cp_async4(vb + tt * COLS + c, xc + (size_t)(g0 + tt) * C + v_at + col0 + c);
+        }
+        for (int idx = tid; idx < nt * 2; idx += 128) {
+            const int tt = idx >> 1, w = idx & 1;
+            cp_async4(gbb + tt * 2 + w, gb + (size_t)(g0 + tt) * 2 * H + (size_t)w * H + h);
+        }
+    };
+    if (t0 < t1) stage(t0, 0);
+    cp_async_commit_();
+    int buf = 0;
+    for (int g0 = t0; g0 < t1; g0 += TB, buf ^= 1) {
+        if (g0 + TB < t1) stage(g0 + TB, buf ^ 1);
+        cp_async_commit_();
+        cp_async_wait_one_();        // this group's copies have landed (the next group's may still fly)
+        __syncthreads();
+        const int nt = min(TB, t1 - g0);
+        const float* kb = dsm_ + buf * BUF;
+        const float* qb = kb + TB * DP;
+        const float* vb = qb + TB * DP;
+        const float* gbb = vb + TB * COLS;
+        for (int tt = 0; tt < nt; ++tt) {
+            const float g = gbb[tt * 2], beta = gbb[tt * 2 + 1], v = vb[tt * COLS + col_local];
+            float kk[DR];
+            float p[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int ii = 0; ii < DR; ++ii) {
+                kk[ii] = kb[tt * DP + r + R * ii];
+                p[ii & 3] = fmaf(kk[ii], S[ii], p[ii & 3]);
+            }
+            float ks = (p[0] + p[1]) + (p[2] + p[3]);
+#pragma unroll
+            for (int m = 1; m < R; m <<= 1) ks += __shfl_xor_sync(0xffffffffu, ks, m);
+            const float u = beta * (v - g * ks);       // S^T k of the decayed state is g times that of the old one
+            float a[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int ii = 0; ii < DR; ++ii) {
+                S[ii] = fmaf(g, S[ii], kk[ii] * u);
+                a[ii & 3] = fmaf(qb[tt * DP + r + R * ii], S[ii], a[ii & 3]);
+            }
+            float os = (a[0] + a[1]) + (a[2] + a[3]);
+#pragma unroll
+            for (int m = 1; m < R; m <<= 1) os += __shfl_xor_sync(0xffffffffu, os, m);
+            if (r == 0 && col < e) o[(size_t)(g0 + tt) * H * e + (size_t)h * e + col] = os;
+        }
+        __syncthreads();             // the buffer is free for the group after next
+    }
+#pragma unroll
+    for (int ii = 0; ii < DR; ++ii) {
+        const int i = r + R * ii;
+        if (i < d && col < e) s_head[(size_t)i * e + col] = S[ii];
+    }
+}
+
+template <int DR, int R>
+static int launch_delta_scan(const float* xc, const float* gb, float* state, long slot_stride, const int* seq_slots, const int* cu_seqlens,
+                             float* o, int n_seqs, int H, int G, int d, int e, cudaStream_t st) {
+    constexpr int DP = DR * R, COLS = 4 * (32 / R), TB = DP <= 256 ? 8 : (DP <= 512 ? 4 : 2);
+    constexpr size_t smem = (size_t)2 * TB * (2 * DP + COLS + 2) * sizeof(float);
+    static_assert(smem <= 48 * 1024, "the staging buffers fit the default shared memory");
+    dim3 grid(n_seqs, H, (e + COLS - 1) / COLS);
+    delta_scan_kernel<DR, R><<<grid, 128, smem, st>>>(xc, gb, state, slot_stride, seq_slots, cu_seqlens, o, H, G, d, e);
+    return 0;
+}
+
+extern "C" int nncpu_delta_scan(const float* xc, const float* gb, float* state, long slot_stride, const int* seq_slots,
+                                const int* cu_seqlens, float* o, int n_seqs, int H, int G, int d, int e, void* stream) {
+    NN_CHECK(n_seqs >= 0 && H > 0 && G > 0 && H % G == 0 && d > 0 && e > 0, "delta scan: %d sequences, %d heads of %d x %d",
+             n_seqs, H, d, e);
+    NN_CHECK(d <= 1024, "delta scan: %d key channels a head (at most 1024)", d);
+    NN_CHECK(H <= 65535 && e <= 65535 * 16, "delta scan: grid");
+    if (n_seqs == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (d <= 32) launch_delta_scan<8, 4>(xc, gb, state, slot_stride, seq_slots, cu_seqlens, o, n_seqs, H, G, d, e, st);
+    else if (d <= 64) launch_delta_scan<16, 4>(xc, gb, state, slot_stride, seq_slots, cu_seqlens, o, n_seqs, H, G, d, e, st);
+    else if (d <= 128) launch_delta_scan<32, 4>(xc, gb, state, slot_stride, seq_slots, cu_seqlens, o, n_seqs, H, G, d, e, st);
+    else if (d <= 256) launch_delta_scan<32, 8>(xc, gb, state, slot_stride, seq_slots, cu_seqlens, o, n_seqs, H, G, d, e, st);
+    else if (d <= 512) launch_delta_scan<32, 16>(xc, gb, state, slot_stride, seq_slots, cu_seqlens, o, n_seqs, H, G, d, e, st);
+    else launch_delta_scan<32, 32>(xc, gb, state, slot_stride, seq_slots, cu_seqlens, o, n_seqs, H, G, d, e, st);
+    NN_LAUNCH_OK("delta scan");
+    return 0;
+}

@@ -114,6 +114,8 @@ def launch_overlap(on: bool) -> None:
         getattr(library.load(name), f"nncpu_launch_overlap_{name}")(ctypes.c_int(1 if on else 0))
 
 
+_l = ctypes.c_long      # a C long: strides in elements
+
 _i = int      # a C int: ctypes passes a Python int as one (sizes, counts, flags, type codes; booleans become 0 or 1)
 
 
@@ -343,8 +345,8 @@ NORM_ROW_WORDS = 16  # 64-bit words of one row's accumulator: 8 bins, a word tha
 NORM_WORDS = 256    # the accumulators of one norm of a few-token step: 16 rows
 
 
-def rope_table(positions, inv_freq, out, position_scale: float = 1.0, by_pair: bool = False) -> None:
-    """out[t, i] = (cos, sin)(positions[t] * position_scale * inv_freq[i]); out float32 [n, half, 2], or with
+def rope_table(positions, inv_freq, out, position_scale: float = 1.0, by_pair: bool = False, stretch: float = 1.0) -> None:
+    """out[t, i] = stretch * (cos, sin)(positions[t] * position_scale * inv_freq[i]); out float32 [n, half, 2], or with
     ``by_pair`` [half, n, 2] holding the same values as out[i, t]."""
     if by_pair:
         half, n, two = out.shape
@@ -353,27 +355,31 @@ def rope_table(positions, inv_freq, out, position_scale: float = 1.0, by_pair: b
     assert two == 2 and out.dtype == torch.float32 and inv_freq.dtype == torch.float32
     assert inv_freq.numel() == half and positions.dtype == torch.int32 and positions.numel() >= n
     _call("generic", "nncpu_rope_table", _ptr(positions), _ptr(inv_freq), _ptr(out), _i(n), _i(half),
-          _f(position_scale), _i(by_pair), _stream())
+          _f(position_scale), _i(by_pair), _f(stretch), _stream())
 
 
 def qk_norm_rope_append(qkv, q_gamma, k_gamma, eps, cos_sin, tok_seq, tok_pos, block_table, k_pages, v_pages,
-                        q_out, n_heads: int, n_kv: int, head_dim: int, v_head_dim: int = 0, q_temp=None) -> None:
+                        q_out, n_heads: int, n_kv: int, head_dim: int, v_head_dim: int = 0, q_temp=None,
+                        values_are_keys: bool = False) -> None:
     """Per-head norm and rotation of q and k, and the append of k and v to
     their pages.  ``n_kv`` 0: qkv holds q only and nothing is appended.  ``v_head_dim``: lanes of a value
     head when they differ from ``head_dim``.  ``q_temp = (coef, every)``: the query at position p is
-    multiplied by 1 + coef * ln(floor((p + 1) / every) + 1)."""
+    multiplied by 1 + coef * ln(floor((p + 1) / every) + 1).  ``values_are_keys``: the rows hold no value heads, a
+    position's value is its key as projected (before norm and rotation).  A row may be longer than its heads."""
     n = q_out.shape[0]
     rot_half = 0 if cos_sin is None else cos_sin.shape[1]
     v_head_dim = v_head_dim or head_dim
     coef, every = q_temp if q_temp is not None else (0.0, 1)
-    assert qkv.shape == (n, (n_heads + n_kv) * head_dim + n_kv * v_head_dim) and q_out.shape == (n, n_heads * head_dim)
+    assert qkv.shape[0] == n and q_out.shape == (n, n_heads * head_dim) and qkv.is_contiguous()
+    assert qkv.shape[1] >= (n_heads + n_kv) * head_dim + (0 if values_are_keys else n_kv * v_head_dim)
     assert q_gamma is None or k_gamma is None or q_gamma.dtype == k_gamma.dtype
     g = q_gamma if q_gamma is not None else k_gamma
     bt_stride = block_table.shape[1] if block_table is not None else 0
     _call("generic", "nncpu_qk_norm_rope_append", _ptr(qkv), _i(_code(qkv)), _ptr(q_gamma), _ptr(k_gamma),
           _i(_code(g)), _f(eps), _ptr(cos_sin), _i(rot_half), _ptr(tok_seq), _ptr(tok_pos), _ptr(block_table),
           _i(bt_stride), _ptr(k_pages), _ptr(v_pages), _i(_code(k_pages)), _ptr(q_out), _i(_code(q_out)), _i(n),
-          _i(n_heads), _i(n_kv), _i(head_dim), _i(v_head_dim), _f(coef), _i(every), _stream())
+          _i(n_heads), _i(n_kv), _i(head_dim), _i(v_head_dim), _f(coef), _i(every), _i(qkv.shape[1]),
+          _i(values_are_keys), _stream())
 
 
 def key_span(window: int = 0, chunk: int = 0) -> int:
@@ -386,18 +392,21 @@ def key_span(window: int = 0, chunk: int = 0) -> int:
 
 
 def attention(q, k_pages, v_pages, block_table, tok_seq, tok_pos, out, n_heads: int, n_kv: int, head_dim: int,
-              scale: float, window: int = 0, v_head_dim: int = 0, slope_base: float = 0.0) -> None:
+              scale: float, window: int = 0, v_head_dim: int = 0, slope_base: float = 0.0, sinks=None) -> None:
     """Causal attention of each token over its sequence's pages.  ``window``: see ``key_span`` (here and in the
     other attention kernels).  ``v_head_dim``: lanes of a value head (and of
     the output) when they differ from ``head_dim``.  ``slope_base`` b != 0: head h takes
-    2^(-b (h + 1) / n_heads) * (query position - key position) off its scaled scores."""
+    2^(-b (h + 1) / n_heads) * (query position - key position) off its scaled scores.  ``sinks`` (float32
+    [n_heads]): exp(sinks[h]) joins the denominator of head h's softmax (here and in the other attention kernels)."""
     n = q.shape[0]
     v_head_dim = v_head_dim or head_dim
     assert q.shape == (n, n_heads * head_dim) and out.shape == (n, n_heads * v_head_dim)
     assert k_pages.dtype == v_pages.dtype and block_table.dtype == torch.int32
+    assert sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == n_heads)
     _call("generic", "nncpu_attention", _ptr(q), _i(_code(q)), _ptr(k_pages), _ptr(v_pages), _i(_code(k_pages)),
           _ptr(block_table), _i(block_table.shape[1]), _ptr(tok_seq), _ptr(tok_pos), _ptr(out), _i(_code(out)),
-          _i(n), _i(n_heads), _i(n_kv), _i(head_dim), _i(v_head_dim), _f(scale), _i(window), _f(slope_base), _stream())
+          _i(n), _i(n_heads), _i(n_kv), _i(head_dim), _i(v_head_dim), _f(scale), _i(window), _f(slope_base), _ptr(sinks),
+          _stream())
 
 
 def attention_mma_supported(n_heads: int, n_kv: int, head_dim: int, *tensors) -> bool:
@@ -535,53 +544,99 @@ def rmsnorm_dual(x, gamma1, eps1: float, gamma2, eps2: float, out1, out2) -> Non
           _ptr(out1), _ptr(out2), _i(_code(out1)), _i(n), _i(dim), _stream())
 
 
-def linear_heads(x, x_col: int, w, out, out_col: int = 0, gate=None, gate_col: int = 0) -> None:
+def linear_heads(x, x_col: int, w, out, out_col: int = 0, gate=None, gate_col: int = 0, x_step: int = 0,
+                 out_step: int = 0) -> None:
     """One product per head: out[t, out_col + b * N : ... + N] = x[t, x_col + b * K : ... + K] . w[b]^T for the heads
     b of w [B, N, K]; x and out are row-major matrices whose rows hold the heads side by side.  With ``gate``
-    (float32 [n, *]) row t of head b is multiplied by sigmoid(gate[t, gate_col + b]).  32-bit on CUDA cores."""
+    (float32 [n, *]) row t of head b is multiplied by sigmoid(gate[t, gate_col + b]).  32-bit on CUDA cores.
+    ``x_step`` / ``out_step``: lanes from one head to the next in a row of x / out when a head there is wider than K / N
+    (only the first K lanes are read, only the first N written)."""
     B, N, K = w.shape
     m = x.shape[0]
-    assert out.shape[0] == m and x.shape[1] >= x_col + B * K and out.shape[1] >= out_col + B * N
+    x_step, out_step = x_step or K, out_step or N
+    assert out.shape[0] == m and x.shape[1] >= x_col + (B - 1) * x_step + K and out.shape[1] >= out_col + (B - 1) * out_step + N
     assert x.is_contiguous() and out.is_contiguous()
     assert gate is None or (gate.dtype == torch.float32 and gate.shape[0] == m and gate.is_contiguous())
     xe, oe = x.element_size(), out.element_size()
     _call("generic", "nncpu_linear_heads", _vp(x.data_ptr() + x_col * xe) if not (x.is_meta and _dry) else None,
           _i(_code(x)), _ptr(w), _i(_code(w)),
           _vp(out.data_ptr() + out_col * oe) if not (out.is_meta and _dry) else None, _i(_code(out)), _i(m), _i(N), _i(K),
-          _i(B), _i(x.shape[1]), _i(out.shape[1]), _i(K), _i(N), _ptr(gate),
+          _i(B), _i(x.shape[1]), _i(out.shape[1]), _i(x_step), _i(out_step), _ptr(gate),
           _i(0 if gate is None else gate.shape[1]), _i(gate_col), _stream())
 
 
-def linear_heads_tc_supported(x, x_col: int, w, out) -> bool:
+def linear_heads_tc_supported(x, x_col: int, w, out, x_step: int = 0) -> bool:
     """Whether ``linear_heads_tc`` takes these operands: bfloat16 x and w, a head's K a multiple of 64, 16-byte steps."""
     B, N, K = w.shape
     return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.dtype in (torch.bfloat16, torch.float32)
-            and x_col == 0 and K % 64 == 0 and x.shape[1] % 8 == 0)
+            and x_col == 0 and K % 64 == 0 and x.shape[1] % 8 == 0 and (x_step or K) % 8 == 0)
 
 
-def linear_heads_tc(x, w, out, workspace: GemmWorkspace, gate=None, gate_col: int = 0) -> None:
+def linear_heads_tc(x, w, out, workspace: GemmWorkspace, gate=None, gate_col: int = 0, x_step: int = 0,
+                    out_step: int = 0) -> None:
     """``linear_heads`` on the tcgen05 tensor cores (the grouped product with the heads as groups): x [n, >= B K]
-    bfloat16 with the heads side by side from column 0, w [B, N, K] bfloat16, out [n, >= B N] from column 0."""
+    bfloat16 with the heads side by side from column 0, w [B, N, K] bfloat16, out [n, >= B N] from column 0.
+    ``x_step`` / ``out_step`` as in ``linear_heads``."""
     B, N, K = w.shape
     m = x.shape[0]
-    assert linear_heads_tc_supported(x, 0, w, out) and out.shape[0] == m and x.shape[1] >= B * K and out.shape[1] >= B * N
+    x_step, out_step = x_step or K, out_step or N
+    assert linear_heads_tc_supported(x, 0, w, out, x_step) and out.shape[0] == m
+    assert x.shape[1] >= (B - 1) * x_step + K and out.shape[1] >= (B - 1) * out_step + N
     assert gate is None or (gate.dtype == torch.float32 and gate.shape[0] == m and gate.is_contiguous())
     _call("gemm_sm100", "nncpu_linear_tc_heads", _ptr(x), _ptr(w), _ptr(out), _i(_code(out)), _i(m), _i(N), _i(K), _i(B),
-          _i(x.shape[1]), _i(out.shape[1]), _i(K), _i(N), _ptr(gate), _i(0 if gate is None else gate.shape[1]), _i(gate_col),
-          _ptr(workspace.status), _stream())
+          _i(x.shape[1]), _i(out.shape[1]), _i(x_step), _i(out_step), _ptr(gate), _i(0 if gate is None else gate.shape[1]),
+          _i(gate_col), _ptr(workspace.status), _stream())
 
 
-def latent_append(proj, col: int, gamma, eps: float, tok_seq, tok_pos, block_table, pages, q_out=None) -> None:
+def latent_append(proj, col: int, gamma, eps: float, tok_seq, tok_pos, block_table, pages, q_out=None, rot_dim: int = 0,
+                  cos_sin=None, q_norm=None) -> None:
     """pages[row of token t] = rmsnorm(proj[t, col : col + rank]) * gamma: the one vector per position that latent
-    attention keeps.  proj float32; pages [n_pages, 1, PAGE, rank].  With ``q_out`` (bfloat16 [n, q_size]) the first
-    q_size columns of proj are left there rounded to bfloat16."""
+    attention keeps.  proj float32; pages [n_pages, 1, PAGE, rank + rot_dim].  With ``q_out`` (bfloat16 [n, q_size])
+    the first q_size columns of proj are left there rounded to bfloat16.  ``rot_dim`` > 0: the rot_dim lanes after the
+    latent's in proj are a key part that all heads share; its first 2 * cos_sin.shape[1] lanes are rotated in
+    neighbouring pairs by ``cos_sin`` [n, pairs, 2] and it follows the latent in the page row.  ``pages`` None: the
+    layer reads another layer's cache, nothing is appended.  ``q_norm = (gamma, col, rank, out)``: the queries' own
+    latent at that column is normed into ``out`` [n, rank]."""
     n = proj.shape[0]
-    rank = pages.shape[-1]
-    assert proj.dtype == torch.float32 and pages.shape[1] == 1 and gamma.numel() == rank
+    assert proj.dtype == torch.float32 and proj.is_contiguous()
+    rank = gamma.numel() if gamma is not None else 1
+    if pages is not None:
+        assert pages.shape[1] == 1 and pages.shape[-1] == rank + rot_dim
     assert q_out is None or (q_out.dtype == torch.bfloat16 and q_out.shape[0] == n and q_out.shape[1] <= proj.shape[1])
-    _call("generic", "nncpu_latent_append", _ptr(proj), _i(proj.shape[1]), _i(col), _ptr(gamma), _i(_code(gamma)), _f(eps),
-          _ptr(tok_seq), _ptr(tok_pos), _ptr(block_table), _i(block_table.shape[1]), _ptr(pages), _i(_code(pages)),
-          _i(n), _i(rank), _ptr(q_out), _i(0 if q_out is None else q_out.shape[1]), _stream())
+    rot_half = 0 if cos_sin is None else cos_sin.shape[1]
+    assert cos_sin is None or (cos_sin.dtype == torch.float32 and cos_sin.shape == (n, rot_half, 2))
+    qg, qcol, qrank, cq = q_norm if q_norm is not None else (None, 0, 0, None)
+    assert q_norm is None or (cq.shape == (n, qrank) and qg.numel() == qrank and cq.is_contiguous()
+                              and (gamma is None or qg.dtype == gamma.dtype))
+    g = gamma if gamma is not None else qg
+    _call("generic", "nncpu_latent_append", _ptr(proj), _i(proj.shape[1]), _i(col), _ptr(gamma), _i(_code(g)), _f(eps),
+          _ptr(tok_seq), _ptr(tok_pos), _ptr(block_table), _i(0 if block_table is None else block_table.shape[1]),
+          _ptr(pages), _i(_code(pages)), _i(n), _i(rank), _ptr(q_out), _i(0 if q_out is None else q_out.shape[1]),
+          _i(rot_dim), _ptr(cos_sin), _i(rot_half), _ptr(qg), _i(qcol), _i(qrank), _ptr(cq), _i(_code(cq)), _stream())
+
+
+def latent_query(q, cos_sin, q_lat, n_heads: int, head_dim: int, rot_dim: int, rank: int, q16=None) -> None:
+    """The rotated part of latent attention's queries: q float32 [n, H (head_dim + rot_dim)] holds per head head_dim
+    unrotated lanes, then rot_dim lanes whose first 2 * cos_sin.shape[1] are rotated in neighbouring pairs by ``cos_sin``
+    [n, pairs, 2]; they go to q_lat[t, head, rank : rank + rot_dim] (rows of H (rank + rot_dim) lanes).  With ``q16``
+    (bfloat16, q's shape) q is also left there rounded."""
+    n = q.shape[0]
+    rot_half = 0 if cos_sin is None else cos_sin.shape[1]
+    assert q.dtype == torch.float32 and q.shape == (n, n_heads * (head_dim + rot_dim)) and q.is_contiguous()
+    assert q_lat.shape == (n, n_heads * (rank + rot_dim)) and q_lat.is_contiguous()
+    assert cos_sin is None or (cos_sin.dtype == torch.float32 and cos_sin.shape == (n, rot_half, 2))
+    assert q16 is None or (q16.dtype == torch.bfloat16 and q16.shape == q.shape and q16.is_contiguous())
+    _call("generic", "nncpu_latent_query", _ptr(q), _i(n), _i(n_heads), _i(head_dim), _i(rot_dim), _ptr(cos_sin),
+          _i(rot_half), _ptr(q_lat), _i(_code(q_lat)), _i(rank), _ptr(q16), _stream())
+
+
+def sigmoid_gate(x, gate, col: int) -> None:
+    """x[t, i] *= sigmoid(gate[t, col + i]) in 32-bit; x [n, width] in either element type, gate float32 [n, >= col + width]."""
+    n, width = x.shape
+    assert gate.dtype == torch.float32 and gate.shape[0] == n and gate.shape[1] >= col + width
+    assert x.is_contiguous() and gate.is_contiguous()
+    _call("generic", "nncpu_sigmoid_gate", _ptr(x), _i(_code(x)), _ptr(gate), _i(gate.shape[1]), _i(col), _i(n), _i(width),
+          _stream())
 
 
 def moe_route(logits, top: int, ids, weights) -> None:
@@ -735,13 +790,53 @@ def gla_scan(proj, z, state, seq_slots, cu_seqlens, o, n_seqs: int, n_heads: int
           _stream())
 
 
-def gla_output(o, proj, weight, eps: float, out, n_heads: int, d: int, e: int) -> None:
-    """out[t, h] = o[t, h] / rms(o[t, h]) * weight * silu(g[t, h]) with g the last H e lanes of ``proj``'s rows."""
+def gla_output(o, proj, weight, eps: float, out, n_heads: int, d: int, e: int, gate_col: int = -1) -> None:
+    """out[t, h] = o[t, h] / rms(o[t, h]) * weight * silu(g[t, h]) with g the H e lanes of ``proj``'s rows from column
+    ``gate_col`` (default: after 2 H d + H e lanes, where gated linear attention keeps them)."""
     n = o.shape[0]
     assert o.dtype == proj.dtype == torch.float32 and o.shape == (n, n_heads * e) and out.shape == o.shape
     assert weight.numel() == e
-    _call("recurrent", "nncpu_gla_output", _ptr(o), _ptr(proj), _i(proj.shape[1]), _i(2 * n_heads * d + n_heads * e),
+    _call("recurrent", "nncpu_gla_output", _ptr(o), _ptr(proj), _i(proj.shape[1]),
+          _i(gate_col if gate_col >= 0 else 2 * n_heads * d + n_heads * e),
           _ptr(weight), _i(_code(weight)), _f(eps), _ptr(out), _i(_code(out)), _i(n), _i(n_heads), _i(e), _stream())
+
+
+def delta_prepare(proj, conv_w, state, conv_col: int, tok_seq, seq_slots, cu_seqlens, a_log, dt_bias, xc, gb, n_seqs: int,
+                  n_heads: int, n_kv: int, d: int, e: int, taps: int) -> None:
+    """What the gated delta rule's recurrence reads, from the projections: ``proj`` float32 [n, >= C + H e + 2 H] holds
+    per token q (G d), k (G d), v (H e) (the C channels of the short convolutions), the output gate's logits (H e), the
+    logits of beta (H) and the decays' inputs (H).  ``xc`` float32 [n, C] receives silu(conv(.)) with q and k made unit
+    vectors per head (q also times d^-1/2), ``gb`` float32 [n, 2 H] the decays exp(-exp(A_log) softplus(a + dt_bias))
+    and then beta = sigmoid(b).  ``conv_w`` [C, taps]; ``state`` float32 [slots, L] holds from lane ``conv_col`` of a
+    slot's row [taps - 1, C]: the sequence's last inputs; it is left advanced by the step's tokens."""
+    n = xc.shape[0]
+    C = 2 * n_kv * d + n_heads * e
+    assert proj.dtype == xc.dtype == gb.dtype == state.dtype == torch.float32 and proj.is_contiguous()
+    assert proj.shape[0] == n and proj.shape[1] >= C + n_heads * e + 2 * n_heads and xc.shape == (n, C)
+    assert gb.shape == (n, 2 * n_heads) and conv_w.shape == (C, taps) and conv_w.is_contiguous()
+    assert state.dim() == 2 and state.shape[1] >= conv_col + (taps - 1) * C and state.is_contiguous()
+    assert a_log.numel() == dt_bias.numel() == n_heads and a_log.dtype == dt_bias.dtype
+    assert tok_seq.dtype == seq_slots.dtype == cu_seqlens.dtype == torch.int32 and cu_seqlens.numel() >= n_seqs + 1
+    _call("recurrent", "nncpu_delta_prepare", _ptr(proj), _i(proj.shape[1]), _ptr(conv_w), _i(_code(conv_w)),
+          None if (state.is_meta and _dry) else _vp(state.data_ptr() + 4 * conv_col), _l(state.shape[1]), _ptr(tok_seq), _ptr(seq_slots), _ptr(cu_seqlens), _ptr(a_log),
+          _ptr(dt_bias), _i(_code(a_log)),
+          _ptr(xc), _ptr(gb), _i(n), _i(n_seqs), _i(n_heads), _i(n_kv), _i(d), _i(e), _i(taps), _f(d ** -0.5), _stream())
+
+
+def delta_scan(xc, gb, state, seq_slots, cu_seqlens, o, n_seqs: int, n_heads: int, n_kv: int, d: int, e: int) -> None:
+    """The gated delta rule over the step's tokens, sequence by sequence in order: per head S <- g S;
+    u = beta (v - S^T k); S <- S + k u^T; o = S^T q, with q, k, v from ``xc`` and g, beta from ``gb`` as
+    ``delta_prepare`` leaves them.  ``state`` float32 [slots, >= H d e] (a slot's [H, d, e] in the first lanes of its
+    row) is read and left updated for the slots in
+    ``seq_slots`` (negative: a padding sequence, zeros out); ``o`` float32 [n, H e]."""
+    n = o.shape[0]
+    assert xc.dtype == gb.dtype == state.dtype == o.dtype == torch.float32
+    assert xc.shape == (n, 2 * n_kv * d + n_heads * e) and gb.shape == (n, 2 * n_heads) and o.shape == (n, n_heads * e)
+    assert state.dim() == 2 and state.shape[1] >= n_heads * d * e and state.is_contiguous()
+    assert xc.is_contiguous() and gb.is_contiguous()
+    assert seq_slots.dtype == torch.int32 and cu_seqlens.dtype == torch.int32 and cu_seqlens.numel() >= n_seqs + 1
+    _call("recurrent", "nncpu_delta_scan", _ptr(xc), _ptr(gb), _ptr(state), _l(state.shape[1]), _ptr(seq_slots), _ptr(cu_seqlens), _ptr(o),
+          _i(n_seqs), _i(n_heads), _i(n_kv), _i(d), _i(e), _stream())
 
 
 def gather_rows(x, rows, out) -> None:

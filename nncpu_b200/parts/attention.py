@@ -14,6 +14,11 @@ of query i and key j), and a query temperature (the query at position p times
 1 + coef * ln(floor((p + 1) / every) + 1)).  Scores, bias and softmax are 32-bit.  Which earlier keys a query sees is
 ``window`` (the last n up to itself) or ``chunk`` (those of its own block of n positions, blocks counted from position
 0 of the sequence) or neither (all); the kernels know it as one number, ``ops.key_span``.
+
+Further options: ``values_are_keys`` (no value projection: a position's value is its key as projected, before norm and
+rotation), ``sink`` (a learned logit per head whose exponential joins the softmax's denominator), ``out_gate`` (the
+concatenated heads times sigmoid(W_g h), lane by lane, before the output projection; W_g's rows ride in the q/k/v
+product) and ``out_bias``.
 """
 from __future__ import annotations
 
@@ -42,16 +47,21 @@ class Attention(Mixer):
         if s.tensor_names not in ("proj", "short"):
             raise UnsupportedModel(f"{s.name}: tensor names of style {s.tensor_names!r}")
         self.v_dim = s.v_head_dim or s.head_dim
+        if s.values_are_keys and self.v_dim != s.head_dim:
+            raise UnsupportedModel(f"{s.name}: values that are the keys have {s.head_dim} lanes, not {self.v_dim}")
         self.q_size = s.n_heads * s.head_dim
         self.kv_size = 0 if reads_other_cache else s.n_kv_heads * s.head_dim
-        self.v_size = 0 if reads_other_cache else s.n_kv_heads * self.v_dim
+        self.v_size = 0 if (reads_other_cache or s.values_are_keys) else s.n_kv_heads * self.v_dim
         self.out_size = s.n_heads * self.v_dim
+        self.gate_size = self.out_size if s.out_gate else 0
+        self.gate_col = self.q_size + self.kv_size + self.v_size      # the gate's logits follow the heads in a row
         # Value heads of their own size are known to the 32-bit kernel alone.  A distance bias or a query temperature
         # keeps a prompt step off the fused q/k/v epilogue of the projection (which knows neither): the temperature is
         # applied where q is made (in a decode step: inside the attention kernel that starts from the projections),
         # the bias inside the attention kernels (tcgen05 for prompts, mma.sync for decode steps and short portions).
         self.plain_core = self.v_dim != s.head_dim
-        self.unfused = self.plain_core or s.slope_base != 0.0 or s.q_temp_coef != 0.0
+        self.unfused = (self.plain_core or s.slope_base != 0.0 or s.q_temp_coef != 0.0 or s.values_are_keys or s.sink
+                        or s.out_gate)
         self.q_temp = (s.q_temp_coef, s.q_temp_every) if s.q_temp_coef != 0.0 else None
         self.position = None if s.position is None else base.build("position", s.position)
         self.span = ops.key_span(s.window, s.chunk)     # what the kernels take as their ``window``
@@ -62,7 +72,9 @@ class Attention(Mixer):
                                                      0 if self.v_dim == s.head_dim else self.v_dim, chunk=s.chunk)
 
     def _proj_names(self):
-        return ["q_proj"] if self.shared_kv else ["q_proj", "k_proj", "v_proj"]
+        if self.shared_kv:
+            return ["q_proj"]
+        return ["q_proj", "k_proj"] if self.spec.values_are_keys else ["q_proj", "k_proj", "v_proj"]
 
     def _tensor(self, proj: str, bias: bool = False) -> str:
         """The file's name of a projection's matrix or bias."""
@@ -70,6 +82,12 @@ class Attention(Mixer):
         if s.tensor_names == "short":
             return f"{s.name}.{proj[0]}" + (".b" if bias else "")
         return f"{s.name}.{proj}." + ("bias" if bias else "weight")
+
+    def _norm_tensor(self, which: str) -> str:
+        s = self.spec
+        if s.tensor_names == "short":
+            return f"{s.qk_norm.name}.{which}.norm"
+        return f"{s.qk_norm.name}.{which}_norm.weight"
 
     def params(self):
         s, p = self.spec, []
@@ -79,30 +97,40 @@ class Attention(Mixer):
             if s.qkv_bias:
                 p.append(ParamSpec(self._tensor(n, bias=True), (sizes[n],)))
         p.append(ParamSpec(self._tensor("o_proj"), (s.hidden_size, self.out_size)))
-        if s.out_bias_optional:
-            p.append(ParamSpec(self._tensor("o_proj", bias=True), (s.hidden_size,), required=False))
+        if s.out_bias or s.out_bias_optional:
+            p.append(ParamSpec(self._tensor("o_proj", bias=True), (s.hidden_size,), required=s.out_bias))
         if s.qk_norm is not None:
-            p.append(ParamSpec(f"{s.qk_norm.name}.q_norm.weight", (s.head_dim,), init=("one_plus_normal", 0.1)))
+            p.append(ParamSpec(self._norm_tensor("q"), (s.head_dim,), init=("one_plus_normal", 0.1)))
             if not self.shared_kv:
-                p.append(ParamSpec(f"{s.qk_norm.name}.k_norm.weight", (s.head_dim,), init=("one_plus_normal", 0.1)))
+                p.append(ParamSpec(self._norm_tensor("k"), (s.head_dim,), init=("one_plus_normal", 0.1)))
+        if s.sink:
+            p.append(ParamSpec(f"{s.name}.sink", (s.n_heads,), init=("normal", 1.0)))
+        if s.out_gate:
+            p.append(ParamSpec(f"{s.name}.g", (self.gate_size, s.hidden_size)))
         return p
 
     def bind(self, tensors, rt):
         s, self.rt = self.spec, rt
         names = self._proj_names()
         ws = [tensors.pop(self._tensor(n)) for n in names]
+        if s.out_gate:
+            ws.append(tensors.pop(f"{s.name}.g"))       # the gate's logits come out of the same product
         self.w_qkv = ws[0] if len(ws) == 1 else torch.cat(ws, dim=0).contiguous()
         del ws
         self.b_qkv = None
         if s.qkv_bias:
             bs = [tensors.pop(self._tensor(n, bias=True)) for n in names]
+            if s.out_gate:
+                bs.append(torch.zeros(self.gate_size, dtype=bs[0].dtype, device=bs[0].device))   # the gate has no bias
             self.b_qkv = bs[0] if len(bs) == 1 else torch.cat(bs, dim=0).contiguous()
+        # the sink logits enter 32-bit softmax arithmetic
+        self.sinks = tensors[f"{s.name}.sink"].to(torch.float32).contiguous() if s.sink else None
         self.w_o = tensors[self._tensor("o_proj")]
         self.b_o = tensors.get(self._tensor("o_proj", bias=True))
         self.q_gamma = self.k_gamma = None
         if s.qk_norm is not None:
-            self.q_gamma = tensors[f"{s.qk_norm.name}.q_norm.weight"]
-            self.k_gamma = tensors.get(f"{s.qk_norm.name}.k_norm.weight")
+            self.q_gamma = tensors[self._norm_tensor("q")]
+            self.k_gamma = tensors.get(self._norm_tensor("k"))
         if self.position is not None:
             self.position.bind(tensors, rt)
 
@@ -131,7 +159,7 @@ class Attention(Mixer):
                 self._attend(ctx, q, cache, attn)
         else:
             # the projections stay in float32 until the per-head norm and the rotation have been applied
-            qkv = rt.empty(n, self.q_size + self.kv_size + self.v_size, dtype=torch.float32)
+            qkv = rt.empty(n, self.q_size + self.kv_size + self.v_size + self.gate_size, dtype=torch.float32)
             with rt.phase("attn_qkv", self.w_qkv, n):
                 rt.linear(x, self.w_qkv, self.b_qkv, qkv)
             with rt.phase("attn_rope"):
@@ -149,9 +177,13 @@ class Attention(Mixer):
                 with rt.phase("attn_rope"):
                     ops.qk_norm_rope_append(qkv, self.q_gamma, self.k_gamma, eps, cos_sin, ctx.tok_seq, ctx.tok_pos,
                                             cache.block_table, cache.k_pages, cache.v_pages, q, s.n_heads,
-                                            0 if self.shared_kv else s.n_kv_heads, s.head_dim, self.v_dim, self.q_temp)
+                                            0 if self.shared_kv else s.n_kv_heads, s.head_dim, self.v_dim, self.q_temp,
+                                            values_are_keys=s.values_are_keys)
                 with self._core_phase(ctx, cache):
                     self._attend(ctx, q, cache, attn)
+            if s.out_gate:
+                with rt.phase("attn_gate"):
+                    ops.sigmoid_gate(attn, qkv, self.gate_col)
         with rt.phase("attn_out", self.w_o, n):
             # the last write into the residual stream: it may leave the next norm its input
             rt.linear(attn, self.w_o, self.b_o, residual, accumulate=not getattr(ctx, "branch_is_fresh", False),
@@ -171,6 +203,8 @@ class Attention(Mixer):
         """Whether this step's attention can start from the float32 projections: a decode step on the tensor-core
         kernel, every lane of a head rotated (or none), norm weights of one type."""
         s = self.spec
+        if s.values_are_keys or s.out_gate or s.sink:
+            return False
         return (not self.plain_core and ctx.is_decode and self.rt.dtype == torch.bfloat16 and cache.k_pages.dtype == torch.bfloat16
                 and ops.attention_mma_supported(s.n_heads, s.n_kv_heads, s.head_dim)
                 and (self.position is None or self.position.half * 2 == s.head_dim)
@@ -201,9 +235,10 @@ class Attention(Mixer):
         decode, tcgen05 prefill for prompts, mma.sync prefill for a few tokens
         per sequence; everything else: the 32-bit kernel."""
         s = self.spec
-        if self.plain_core or not ops.attention_mma_supported(s.n_heads, s.n_kv_heads, s.head_dim, q, cache.k_pages, attn):
+        if (self.plain_core or self.sinks is not None
+                or not ops.attention_mma_supported(s.n_heads, s.n_kv_heads, s.head_dim, q, cache.k_pages, attn)):
             ops.attention(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.tok_seq, ctx.tok_pos, attn,
-                          s.n_heads, s.n_kv_heads, s.head_dim, s.scale, self.span, self.v_dim, s.slope_base)
+                          s.n_heads, s.n_kv_heads, s.head_dim, s.scale, self.span, self.v_dim, s.slope_base, self.sinks)
         elif ctx.is_decode:
             n_splits, scratch = self._decode_splits(ctx)
             ops.attention_decode_mma(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.tok_seq, ctx.tok_pos,

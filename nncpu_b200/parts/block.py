@@ -181,7 +181,8 @@ class ParallelBlock(Block):
 
     The two norms are of the same rows, so they run as one kernel that takes the sum of squares once; both outputs are
     made before the mixer adds into the stream.  A layer without a feed-forward has the mixer alone (a ``norm2``
-    tensor that its file may still hold is accepted and not used).  The sublayers add into the 32-bit stream one
+    tensor that its file may still hold is accepted and not used).  A layer with a feed-forward and no second norm has
+    ONE norm: x += mixer(h) + feed_forward(h) with h = norm1(x).  The sublayers add into the 32-bit stream one
     after the other."""
 
     def __init__(self, spec, reads_other_cache: bool = False):
@@ -189,7 +190,9 @@ class ParallelBlock(Block):
         self.norm1 = base.build("norm", spec.norm1)
         self.mixer = base.build("mixer", spec.mixer, **kwargs)
         self.feed_forward = None if spec.feed_forward is None else base.build("feed_forward", spec.feed_forward)
-        self.norm2 = None if self.feed_forward is None else base.build("norm", spec.norm2)
+        # with a feed-forward and no second norm, both sublayers read the one norm's output
+        self.norm2 = None if (self.feed_forward is None or spec.norm2 is None) else base.build("norm", spec.norm2)
+        self.one_norm = self.feed_forward is not None and spec.norm2 is None
         # a layer without a feed-forward may still name its second norm: the tensor is then optional
         self._spare = spec.norm2.name + spec.norm2.suffix if (self.feed_forward is None and spec.norm2 is not None) else None
         self._parts = tuple(p for p in (self.norm1, self.mixer, self.norm2, self.feed_forward) if p is not None)
@@ -214,7 +217,8 @@ class ParallelBlock(Block):
     def _norms(self, ctx, residual):
         n1, n2, rt = self.norm1, self.norm2, self.rt
         if n2 is None:
-            return n1.forward(ctx, residual), None
+            x1 = n1.forward(ctx, residual)
+            return x1, (x1 if self.one_norm else None)
         if (getattr(n1, "offset", 1.0) == 0.0 and getattr(n2, "offset", 1.0) == 0.0 and n1.size == n2.size
                 and n1.gamma.dtype == n2.gamma.dtype and residual.dtype == torch.float32):
             x1, x2 = rt.empty(*residual.shape), rt.empty(*residual.shape)
