@@ -14,8 +14,9 @@ with host token ids in and out.  The line also carries a prefill measurement (on
 64, and the SM clocks sampled during the timed region.
 
 ``--workload NAME`` runs another measurement instead and prints its own JSON: ``14b-unequal``, ``32b`` and
-``long-context`` (larger Qwen3 sizes end to end), and ``romepel`` / ``zevivik`` (those designs at two widths beside Qwen3
-layers of equal size: a 2 048-token prompt, decode at batch 8, and every phase's time and roofline fraction).
+``long-context`` (larger Qwen3 sizes end to end), ``romepel`` / ``zevivik`` (those designs at two widths beside Qwen3
+layers of equal size: a 2 048-token prompt, decode at batch 8, and every phase's time and roofline fraction), and
+``pikalorn`` (that design at two widths beside Zevivik and Romepel layers of equal size, measured the same way).
 """
 from __future__ import annotations
 
@@ -234,6 +235,7 @@ WORKLOADS = {
     "long-context": dict(model="8b"),
     "romepel": dict(model="8b"),
     "zevivik": dict(model="8b"),
+    "pikalorn": dict(model="8b"),
 }
 
 # `--workload romepel`: the Romepel design (recurrent gla layers, windowed attention with a distance bias, sandwich
@@ -299,6 +301,73 @@ def zevivik_configs(z: dict):
                                  intermediate_size=z["inter"], vocab_size=z["vocab"], use_sliding_window=True,
                                  sliding_window=z["window"], max_window_layers=0))
     return zev, qwen
+
+
+# `--workload pikalorn`: the Pikalorn design (one-norm parallel layers; attention with sinks, values that are the keys
+# and an output gate; latent attention with a query latent, a shared rotated key part and sinks, every other one of
+# them reading the cache of the one before; the gated delta rule) at sizes that resemble a real model's layers, beside
+# the two closest existing designs at equal width, depth, head counts and feed-forward width: Zevivik (attention and
+# latent attention, where Pikalorn has a recurrent layer: attention) and Romepel (its recurrent gla layers at the places
+# of the delta layers, attention elsewhere).
+PIKALORN_SIZES = {
+    "2048": dict(width=2048, layers=8, heads=16, kv_heads=4, dim=128, inter=6144, lat_heads=16, lat_dim=64, rot_dim=64,
+                 lat_vdim=128, rank=64, q_rank=768, delta_heads=16, delta_kv=8, delta_dim=128, delta_vdim=128, conv=4,
+                 vocab=32768),
+    "4096": dict(width=4096, layers=8, heads=32, kv_heads=8, dim=128, inter=12288, lat_heads=32, lat_dim=64, rot_dim=64,
+                 lat_vdim=128, rank=64, q_rank=1536, delta_heads=32, delta_kv=16, delta_dim=128, delta_vdim=128, conv=4,
+                 vocab=65536),
+}
+
+
+def pikalorn_configs(z: dict):
+    """(Pikalorn configuration, Zevivik's and Romepel's of equal size).  Eight layers: attention, latent, delta, latent
+    on the second layer's cache, and the same four again."""
+    from nncpu_b200.config import config_from_dict
+    dense = {"kind": "dense", "ff": z["inter"]}
+    rot = {"base": 1000000.0, "dims": z["dim"]}
+    lrot = {"base": 10000.0, "dims": z["rot_dim"], "scaling": {"factor": 8.0, "original": 1024, "fast": 32.0, "slow": 1.0}}
+
+    def att():
+        return {"type": "attention", "mlp": dense,
+                "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
+                          "scale": z["dim"] ** -0.5, "rot": rot}}
+
+    def lat(kv_from=None):
+        m = {"heads": z["lat_heads"], "dim": z["lat_dim"], "rot_dim": z["rot_dim"], "vdim": z["lat_vdim"],
+             "kv_rank": z["rank"], "q_rank": z["q_rank"], "scale": (z["lat_dim"] + z["rot_dim"]) ** -0.5, "rot": lrot}
+        if kv_from is not None:
+            m["kv_from"] = kv_from
+        return {"type": "latent_attention", "mlp": dense, "mixer": m}
+
+    def delta():
+        return {"type": "delta", "mlp": dense,
+                "mixer": {"heads": z["delta_heads"], "kv_heads": z["delta_kv"], "dim": z["delta_dim"],
+                          "vdim": z["delta_vdim"], "conv": z["conv"]}}
+
+    assert z["layers"] % 4 == 0
+    layers = []
+    for i in range(0, z["layers"], 4):
+        layers += [att(), lat(), delta(), lat(kv_from=i + 1)]
+    pik = config_from_dict({"architecture": "Pikalorn", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+                            "embedding": {"scale": 1.0}, "layers": layers})
+    zatt = {"type": "attention", "mlp": dense,
+            "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
+                      "scale": z["dim"] ** -0.5, "rot": rot}}
+    zlat = {"type": "latent_attention", "mlp": dense,
+            "mixer": {"heads": z["lat_heads"], "dim": z["lat_dim"] + z["rot_dim"], "vdim": z["lat_vdim"],
+                      "kv_rank": z["rank"] + z["rot_dim"], "scale": (z["lat_dim"] + z["rot_dim"]) ** -0.5}}
+    zev = config_from_dict({"architecture": "Zevivik", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+                            "embedding": {"scale": 1.0}, "layers": [zatt, zlat] * (z["layers"] // 2)})
+    ratt = {"type": "attention", "mlp": {"kind": "dense", "ff": z["inter"] * 3 // 2},
+            "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
+                      "scale": z["dim"] ** -0.5}}
+    rgla = {"type": "gla", "mlp": {"kind": "dense", "ff": z["inter"] * 3 // 2},
+            "mixer": {"heads": z["delta_heads"], "dim": z["delta_dim"], "vdim": z["delta_vdim"], "tau": 8.0,
+                      "rank": z["width"] // 64}}
+    rom = config_from_dict({"architecture": "Romepel", "vocab": z["vocab"], "width": z["width"], "max_positions": CONTEXT,
+                            "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
+                            "layers": [rgla if i % 4 == 2 else ratt for i in range(z["layers"])]})
+    return pik, zev, rom
 
 
 def phase_table(totals: dict, calls: int, pk: dict) -> dict:
@@ -391,6 +460,18 @@ def run_zevivik() -> dict:
         zev, qwen = zevivik_configs(z)
         out["sizes"][name] = {"config": z, "zevivik": run_design_point(zev, z["vocab"], pk),
                               "qwen3_same_size": run_design_point(qwen, z["vocab"], pk)}
+    return out
+
+
+def run_pikalorn() -> dict:
+    pk = peaks()
+    out = {"workload": "pikalorn", "dtype": "bf16", "peaks": pk["source"], "prompt": PROMPT,
+           "data": "synthetic: random weights, uniform random token ids", "sizes": {}}
+    for name, z in PIKALORN_SIZES.items():
+        pik, zev, rom = pikalorn_configs(z)
+        out["sizes"][name] = {"config": z, "pikalorn": run_design_point(pik, z["vocab"], pk),
+                              "zevivik_same_size": run_design_point(zev, z["vocab"], pk),
+                              "romepel_same_size": run_design_point(rom, z["vocab"], pk)}
     return out
 
 
@@ -558,7 +639,8 @@ def main() -> int:
         print(json.dumps(fp32_check(cfg, args.model)))
         return 0
     if args.workload:
-        special = {"long-context": run_long_context, "romepel": run_romepel, "zevivik": run_zevivik}
+        special = {"long-context": run_long_context, "romepel": run_romepel, "zevivik": run_zevivik,
+                   "pikalorn": run_pikalorn}
         print(json.dumps(special[args.workload]() if args.workload in special else run_workload(args.workload)))
         return 0
     model = Model.random(cfg, seed=0, dtype="bfloat16", device="cuda:0")

@@ -75,7 +75,8 @@ __device__ __forceinline__ float ld_cluster_(const float* local, uint32_t rank) 
 // Merges the splits of every (token, head) in split order.  grid = (n_heads, n_tok), HD threads.
 template <int HD>
 __global__ void merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                             __nv_bfloat16* __restrict__ out, int n_heads, int n_kv, int n_splits) {
+                             __nv_bfloat16* __restrict__ out, int n_heads, int n_kv, int n_splits,
+                             const float* __restrict__ sinks) {
     const int h = blockIdx.x, t = blockIdx.y, d = threadIdx.x;
     const int G = n_heads / n_kv, kvh = h / G, head = h % G;
     const size_t pb = ((size_t)t * n_kv + kvh) * n_splits;
@@ -88,6 +89,7 @@ __global__ void merge_kernel(const float* __restrict__ part_o, const float* __re
         o = fmaf(part_o[((pb + s) * G + head) * HD + d], c, o);
         l = fmaf(part_ml[((pb + s) * G + head) * 2 + 1], c, l);
     }
+    if (sinks != nullptr && l > 0.0f) l += exp2f(sinks[h] * kLog2e - m);
     out[((size_t)t * n_heads + h) * HD + d] = __float2bfloat16_rn(l > 0.0f ? o / l : 0.0f);
 }
 
@@ -126,7 +128,8 @@ __global__ void __launch_bounds__(128, 3)
 prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
                const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ block_table, int bt_stride,
                const int* __restrict__ cu_seqlens, const int* __restrict__ tok_pos, __nv_bfloat16* __restrict__ out,
-               int n_seqs, int n_heads, int n_kv, float scale2, int window, float slope_base) {
+               int n_seqs, int n_heads, int n_kv, float scale2, int window, float slope_base,
+               const float* __restrict__ sinks) {
     constexpr int kTileBytes = kPage * HD * 2;           // one page of K or of V for one head
     constexpr int kChunks = HD / 8;                      // 16-byte chunks per row
     extern __shared__ __align__(128) uint8_t fa_smem[];  // [2 stages][K tile | V tile]
@@ -300,6 +303,8 @@ prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
         l[row] += __shfl_xor_sync(0xffffffffu, l[row], 1);
         l[row] += __shfl_xor_sync(0xffffffffu, l[row], 2);
         if (!(row == 0 ? has_lo : has_hi)) continue;
+        // a sink: one more term of the denominator, with no key and no value (the softmax works in powers of two)
+        if (sinks != nullptr && l[row] > 0.0f) l[row] += exp2f(sinks[h] * kLog2e - m[row]);
         const float inv = l[row] > 0.0f ? 1.0f / l[row] : 0.0f;
         __nv_bfloat16* dst = out + (size_t)(q0 + (row == 0 ? row_lo : row_hi)) * n_heads * HD + (size_t)h * HD;
 #pragma unroll
@@ -394,7 +399,7 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restri
                    const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ block_table, int bt_stride,
                    const int* __restrict__ tok_seq, const int* __restrict__ tok_pos, __nv_bfloat16* __restrict__ out,
                    float* __restrict__ part_o, float* __restrict__ part_ml, int n_heads, int n_kv, float scale2,
-                   int window, const FusedQK f) {
+                   int window, const FusedQK f, const float* __restrict__ sinks) {
     constexpr int kTileBytes = kPage * HD * 2;
     constexpr int kChunks = HD / 8;
     constexpr int W = HD + 2;
@@ -622,6 +627,7 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restri
             ll = fmaf(sm[(w * G + head) * W + HD + 1], cw, ll);
         }
         if (n_splits == 1) {
+            if (sinks != nullptr && ll > 0.0f) ll += exp2f(sinks[kvh * G + head] * kLog2e - mm);
             out[out_row + i] = __float2bfloat16_rn(ll > 0.0f ? oo / ll : 0.0f);
         } else if (kCluster) {
             merged[head * W + d] = oo;
@@ -667,6 +673,7 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restri
                     ll = fmaf(ls[sp], cs, ll);
                 }
             }
+            if (sinks != nullptr && ll > 0.0f) ll += exp2f(sinks[kvh * G + head] * kLog2e - mm);
             out[out_row + i] = __float2bfloat16_rn(ll > 0.0f ? oo / ll : 0.0f);
         }
         cluster_barrier_();   // no block leaves while its result may still be read
@@ -677,9 +684,9 @@ template <int HD>
 int launch_decode(const void* q, const void* k_pages, const void* v_pages, const int* block_table, int bt_stride,
                   const int* tok_seq, const int* tok_pos, void* out, float* scratch, int n_tok, int n_heads, int n_kv,
                   float scale, int window, int n_splits, cudaStream_t stream, const FusedQK* fused = nullptr,
-                  float slope_base = 0.0f) {
+                  float slope_base = 0.0f, const float* sinks = nullptr) {
     using Kernel = void (*)(const __nv_bfloat16*, const __nv_bfloat16*, const __nv_bfloat16*, const int*, int, const int*,
-                            const int*, __nv_bfloat16*, float*, float*, int, int, float, int, const FusedQK);
+                            const int*, __nv_bfloat16*, float*, float*, int, int, float, int, const FusedQK, const float*);
     const int G = n_heads / n_kv;
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)n_tok * n_kv * n_splits * G * HD : nullptr;
@@ -715,12 +722,13 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, const
     cfg.numAttrs = cluster ? 1 : 0;
     const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages,
                                              (const __nv_bfloat16*)v_pages, block_table, bt_stride, tok_seq, tok_pos,
-                                             (__nv_bfloat16*)out, part_o, part_ml, n_heads, n_kv, scale * kLog2e, window, f);
+                                             (__nv_bfloat16*)out, part_o, part_ml, n_heads, n_kv, scale * kLog2e, window, f,
+                                             sinks);
     NN_CHECK(e == cudaSuccess, "attention decode (%d splits%s): launch failed: %s", n_splits, cluster ? ", cluster" : "",
              cudaGetErrorString(e));
     if (n_splits > 1 && !cluster) {
         merge_kernel<HD><<<dim3(n_heads, n_tok), HD, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, n_heads, n_kv,
-                                                                  n_splits);
+                                                                  n_splits, sinks);
         NN_LAUNCH_OK("attention merge");
     }
     return 0;
@@ -729,7 +737,7 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, const
 template <int HD>
 int launch_prefill(const void* q, const void* k_pages, const void* v_pages, const int* block_table, int bt_stride,
                    const int* cu_seqlens, const int* tok_pos, void* out, int n_tok, int n_seqs, int n_heads, int n_kv,
-                   float scale, int window, float slope_base, cudaStream_t stream) {
+                   float scale, int window, float slope_base, const float* sinks, cudaStream_t stream) {
     const int max_tiles = n_tok / 64 + n_seqs;
     constexpr int smem = 2 * 2 * kPage * HD * 2;
     static bool configured[64] = {};
@@ -741,7 +749,7 @@ int launch_prefill(const void* q, const void* k_pages, const void* v_pages, cons
     prefill_kernel<HD><<<grid, 128, smem, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages,
                                                  (const __nv_bfloat16*)v_pages, block_table, bt_stride, cu_seqlens,
                                                  tok_pos, (__nv_bfloat16*)out, n_seqs, n_heads, n_kv, scale * kLog2e,
-                                                 window, slope_base);
+                                                 window, slope_base, sinks);
     NN_LAUNCH_OK("attention prefill");
     return 0;
 }
@@ -766,7 +774,7 @@ extern "C" int nncpu_attention_decode_mma(const void* q, const void* k_pages, co
                                           const int* block_table, int bt_stride, const int* tok_seq,
                                           const int* tok_pos, void* out, float* scratch, long scratch_floats,
                                           int n_tok, int n_heads, int n_kv, int hd, float scale, int window,
-                                          int n_splits, float slope_base, void* stream) {
+                                          int n_splits, float slope_base, const float* sinks, void* stream) {
     NN_CHECK(nncpu_attention_mma_supported(n_heads, n_kv, hd),
              "attention (tensor cores): %d heads over %d key/value heads of size %d is not supported "
              "(head size 64 or 128, at most 16 heads per key/value head)", n_heads, n_kv, hd);
@@ -781,9 +789,9 @@ extern "C" int nncpu_attention_decode_mma(const void* q, const void* k_pages, co
     if (n_tok == 0) return 0;
     if (hd == 64)
         return launch_decode<64>(q, k_pages, v_pages, block_table, bt_stride, tok_seq, tok_pos, out, scratch, n_tok,
-                                 n_heads, n_kv, scale, window, n_splits, (cudaStream_t)stream, nullptr, slope_base);
+                                 n_heads, n_kv, scale, window, n_splits, (cudaStream_t)stream, nullptr, slope_base, sinks);
     return launch_decode<128>(q, k_pages, v_pages, block_table, bt_stride, tok_seq, tok_pos, out, scratch, n_tok,
-                              n_heads, n_kv, scale, window, n_splits, (cudaStream_t)stream, nullptr, slope_base);
+                              n_heads, n_kv, scale, window, n_splits, (cudaStream_t)stream, nullptr, slope_base, sinks);
 }
 
 // The same from the float32 projections: qkv [n_tok, per_tok * hd] holds, per token, the heads of q and, if `append`,
@@ -837,7 +845,8 @@ extern "C" int nncpu_attention_decode_mma_from_qkv(const float* qkv, const void*
 extern "C" int nncpu_attention_prefill_mma(const void* q, const void* k_pages, const void* v_pages,
                                            const int* block_table, int bt_stride, const int* cu_seqlens,
                                            const int* tok_pos, void* out, int n_tok, int n_seqs, int n_heads,
-                                           int n_kv, int hd, float scale, int window, float slope_base, void* stream) {
+                                           int n_kv, int hd, float scale, int window, float slope_base, const float* sinks,
+                                           void* stream) {
     NN_CHECK(nncpu_attention_mma_supported(n_heads, n_kv, hd),
              "attention (tensor cores): %d heads over %d key/value heads of size %d is not supported "
              "(head size 64 or 128, at most 16 heads per key/value head)", n_heads, n_kv, hd);
@@ -845,9 +854,9 @@ extern "C" int nncpu_attention_prefill_mma(const void* q, const void* k_pages, c
     if (n_tok == 0 || n_seqs == 0) return 0;
     if (hd == 64)
         return launch_prefill<64>(q, k_pages, v_pages, block_table, bt_stride, cu_seqlens, tok_pos, out, n_tok, n_seqs,
-                                  n_heads, n_kv, scale, window, slope_base, (cudaStream_t)stream);
+                                  n_heads, n_kv, scale, window, slope_base, sinks, (cudaStream_t)stream);
     return launch_prefill<128>(q, k_pages, v_pages, block_table, bt_stride, cu_seqlens, tok_pos, out, n_tok, n_seqs,
-                               n_heads, n_kv, scale, window, slope_base, (cudaStream_t)stream);
+                               n_heads, n_kv, scale, window, slope_base, sinks, (cudaStream_t)stream);
 }
 
 // ---------------------------------------------------------------------------
@@ -927,5 +936,5 @@ extern "C" int nncpu_attention_decode_mma_static(const void* q, const void* k_pa
     float* scratch = nullptr;
     if (int e = static_scratch(&scratch)) return e;
     return nncpu_attention_decode_mma(q, k_pages, v_pages, block_table, bt_stride, tok_seq, tok_pos, out, scratch,
-                                      kStaticScratchFloats, n_tok, n_heads, n_kv, hd, scale, window, n_splits, 0.0f, stream);
+                                      kStaticScratchFloats, n_tok, n_heads, n_kv, hd, scale, window, n_splits, 0.0f, nullptr, stream);
 }

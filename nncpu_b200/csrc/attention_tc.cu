@@ -61,6 +61,7 @@ struct AttnParams {
     float scale2;   // softmax scale times log2(e)
     int window;
     float slope_base;   // b != 0: head h takes 2^(-b (h + 1) / n_heads) * (query position - key position) off its scaled scores
+    const float* sinks; // float32 [n_heads] or null: exp(sinks[h]) joins the denominator of head h's softmax, with no key and no value
     int* status;
 };
 
@@ -439,6 +440,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         }
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // the sink's term, in the unit of the row's sums: powers of two relative to the reference maximum
+            if (p.sinks != nullptr && l > 0.0f) l += exp2f(p.sinks[h] * 1.4426950408889634f - m_ref);
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             __nv_bfloat16* dst = p.out + (size_t)(q0 + row) * ((size_t)p.n_heads * HD) + (size_t)h * HD;
 #pragma unroll 1
@@ -557,8 +560,8 @@ extern "C" int nncpu_attention_prefill_tc_supported(int n_heads, int n_kv, int h
 extern "C" int nncpu_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, int n_pages,
                                           const int* block_table, int bt_stride, const int* cu_seqlens,
                                           const int* tok_pos, void* out, int n_tok, int n_seqs, int n_heads, int n_kv,
-                                          int head_dim, float scale, int window, float slope_base, int* status,
-                                          void* stream_) {
+                                          int head_dim, float scale, int window, float slope_base, const float* sinks,
+                                          int* status, void* stream_) {
     NN_CHECK(nncpu_attention_prefill_tc_supported(n_heads, n_kv, head_dim),
              "attention (tensor cores): head size %d with %d heads over %d key/value heads is not supported "
              "(head size 64 or 128, heads a multiple of key/value heads)", head_dim, n_heads, n_kv);
@@ -584,6 +587,7 @@ extern "C" int nncpu_attention_prefill_tc(const void* q, const void* k_pages, co
     p.scale2 = scale * 1.4426950408889634f;
     p.window = window;
     p.slope_base = slope_base;
+    p.sinks = sinks;
     p.status = status;
     cudaStream_t stream = (cudaStream_t)stream_;
     // two heads to a block where a key/value head has two to give; one head per block otherwise

@@ -438,19 +438,22 @@ def attention_decode_scratch_floats(n_tok: int, n_heads: int, n_kv: int, head_di
 
 
 def attention_decode_mma(q, k_pages, v_pages, block_table, tok_seq, tok_pos, out, scratch, n_heads: int, n_kv: int,
-                         head_dim: int, scale: float, window: int, n_splits: int, slope_base: float = 0.0) -> None:
+                         head_dim: int, scale: float, window: int, n_splits: int, slope_base: float = 0.0,
+                         sinks=None) -> None:
     """One token per sequence; each token's keys are cut into ``n_splits``
     splits that run in parallel.  With ``scratch`` (float32,
     ``attention_decode_scratch_floats`` elements) a second kernel merges them;
     with ``scratch`` None and at most 8 splits they form a thread-block
-    cluster and merge through distributed shared memory."""
+    cluster and merge through distributed shared memory.  ``sinks`` as in ``attention``: the term joins where the
+    splits merge, once."""
     n = q.shape[0]
     assert q.shape == (n, n_heads * head_dim) and out.shape == q.shape
     assert scratch is None or scratch.dtype == torch.float32
+    assert sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == n_heads)
     _call("attention_mma", "nncpu_attention_decode_mma", _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
           _i(block_table.shape[1]), _ptr(tok_seq), _ptr(tok_pos), _ptr(out), _ptr(scratch),
           ctypes.c_long(0 if scratch is None else scratch.numel()), _i(n), _i(n_heads), _i(n_kv), _i(head_dim),
-          _f(scale), _i(window), _i(n_splits), _f(slope_base), _stream())
+          _f(scale), _i(window), _i(n_splits), _f(slope_base), _ptr(sinks), _stream())
 
 
 def attention_decode_mma_from_qkv(qkv, q_gamma, k_gamma, eps, cos_sin, k_pages, v_pages, append: bool, block_table,
@@ -478,13 +481,16 @@ def attention_decode_mma_from_qkv(qkv, q_gamma, k_gamma, eps, cos_sin, k_pages, 
 
 
 def attention_prefill_mma(q, k_pages, v_pages, block_table, cu_seqlens, tok_pos, out, n_seqs: int, n_heads: int,
-                          n_kv: int, head_dim: int, scale: float, window: int, slope_base: float = 0.0) -> None:
-    """Any number of new tokens per sequence, at consecutive positions.  ``slope_base`` as in ``attention``."""
+                          n_kv: int, head_dim: int, scale: float, window: int, slope_base: float = 0.0,
+                          sinks=None) -> None:
+    """Any number of new tokens per sequence, at consecutive positions.  ``slope_base`` and ``sinks`` as in
+    ``attention``."""
     n = q.shape[0]
     assert q.shape == (n, n_heads * head_dim) and out.shape == q.shape and cu_seqlens.numel() >= n_seqs + 1
+    assert sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == n_heads)
     _call("attention_mma", "nncpu_attention_prefill_mma", _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
           _i(block_table.shape[1]), _ptr(cu_seqlens), _ptr(tok_pos), _ptr(out), _i(n), _i(n_seqs), _i(n_heads),
-          _i(n_kv), _i(head_dim), _f(scale), _i(window), _f(slope_base), _stream())
+          _i(n_kv), _i(head_dim), _f(scale), _i(window), _f(slope_base), _ptr(sinks), _stream())
 
 
 def attention_prefill_tc_supported(n_heads: int, n_kv: int, head_dim: int, *tensors) -> bool:
@@ -495,10 +501,12 @@ def attention_prefill_tc_supported(n_heads: int, n_kv: int, head_dim: int, *tens
 
 
 def attention_prefill_tc(q, k_pages, v_pages, block_table, cu_seqlens, tok_pos, out, status, n_seqs: int,
-                         n_heads: int, n_kv: int, head_dim: int, scale: float, window: int, slope_base: float = 0.0) -> None:
+                         n_heads: int, n_kv: int, head_dim: int, scale: float, window: int, slope_base: float = 0.0,
+                         sinks=None) -> None:
     """Prefill attention on the tcgen05 tensor cores: any number of new tokens per sequence, at consecutive
     positions; ``status`` is an int32 word on the device that receives a code if a bounded wait runs out.
-    ``slope_base`` as in ``attention``."""
+    ``slope_base`` and ``sinks`` as in ``attention``."""
+    assert sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == n_heads)
     n = q.shape[0]
     assert q.shape == (n, n_heads * head_dim) and out.shape == q.shape and cu_seqlens.numel() >= n_seqs + 1
     assert q.is_contiguous() and out.is_contiguous() and k_pages.is_contiguous() and v_pages.is_contiguous()
@@ -506,7 +514,8 @@ def attention_prefill_tc(q, k_pages, v_pages, block_table, cu_seqlens, tok_pos, 
     assert status.dtype == torch.int32
     _call("attention_tc", "nncpu_attention_prefill_tc", _ptr(q), _ptr(k_pages), _ptr(v_pages), _i(k_pages.shape[0]),
           _ptr(block_table), _i(block_table.shape[1]), _ptr(cu_seqlens), _ptr(tok_pos), _ptr(out), _i(n), _i(n_seqs),
-          _i(n_heads), _i(n_kv), _i(head_dim), _f(scale), _i(window), _f(slope_base), _ptr(status), _stream())
+          _i(n_heads), _i(n_kv), _i(head_dim), _f(scale), _i(window), _f(slope_base), _ptr(sinks),
+          _ptr(status), _stream())
 
 
 GATED_ACTS = {"silu": 0, "gelu_tanh": 1, "swish_clamp": 2}

@@ -235,7 +235,7 @@ class Attention(Mixer):
         decode, tcgen05 prefill for prompts, mma.sync prefill for a few tokens
         per sequence; everything else: the 32-bit kernel."""
         s = self.spec
-        if (self.plain_core or self.sinks is not None
+        if (self.plain_core
                 or not ops.attention_mma_supported(s.n_heads, s.n_kv_heads, s.head_dim, q, cache.k_pages, attn)):
             ops.attention(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.tok_seq, ctx.tok_pos, attn,
                           s.n_heads, s.n_kv_heads, s.head_dim, s.scale, self.span, self.v_dim, s.slope_base, self.sinks)
@@ -243,15 +243,15 @@ class Attention(Mixer):
             n_splits, scratch = self._decode_splits(ctx)
             ops.attention_decode_mma(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.tok_seq, ctx.tok_pos,
                                      attn, scratch, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, self.span, n_splits,
-                                     s.slope_base)
+                                     s.slope_base, self.sinks)
         elif ctx.n_tokens >= 32 * ctx.n_seqs and ops.attention_prefill_tc_supported(
                 s.n_heads, s.n_kv_heads, s.head_dim, q, cache.k_pages, attn):
             # prompts: 128-row tiles on the tcgen05 tensor cores
             ops.attention_prefill_tc(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.cu_seqlens, ctx.tok_pos,
                                      attn, self.rt.workspace.status, ctx.n_seqs, s.n_heads, s.n_kv_heads, s.head_dim,
-                                     s.scale, self.span, s.slope_base)
+                                     s.scale, self.span, s.slope_base, self.sinks)
         else:
             # a few new tokens per sequence: 64-row tiles
             ops.attention_prefill_mma(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.cu_seqlens, ctx.tok_pos,
                                       attn, ctx.n_seqs, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, self.span,
-                                      s.slope_base)
+                                      s.slope_base, self.sinks)

@@ -183,7 +183,7 @@ class LatentAttention(Mixer):
 
     def _tensor_core_attention(self, cache) -> bool:
         s = self.spec
-        return (self.sinks is None and self.rt.dtype == torch.bfloat16 and cache.k_pages.dtype == torch.bfloat16
+        return (self.rt.dtype == torch.bfloat16 and cache.k_pages.dtype == torch.bfloat16
                 and ops.attention_mma_supported(s.n_heads, 1, self.row))
 
     def _core_phase(self, ctx, cache):
@@ -208,10 +208,10 @@ class LatentAttention(Mixer):
                 ctx.n_tokens, H, 1, r, n_splits)
             scratch = rt.empty(floats, dtype=torch.float32) if floats else None
             ops.attention_decode_mma(q, pages, pages, cache.block_table, ctx.tok_seq, ctx.tok_pos, out, scratch, H, 1, r,
-                                     s.scale, 0, n_splits)
+                                     s.scale, 0, n_splits, 0.0, self.sinks)
         elif ctx.n_tokens >= 32 * ctx.n_seqs and ops.attention_prefill_tc_supported(H, 1, r, q, pages, out):
             ops.attention_prefill_tc(q, pages, pages, cache.block_table, ctx.cu_seqlens, ctx.tok_pos, out,
-                                     rt.workspace.status, ctx.n_seqs, H, 1, r, s.scale, 0)
+                                     rt.workspace.status, ctx.n_seqs, H, 1, r, s.scale, 0, 0.0, self.sinks)
         else:
             ops.attention_prefill_mma(q, pages, pages, cache.block_table, ctx.cu_seqlens, ctx.tok_pos, out, ctx.n_seqs,
-                                      H, 1, r, s.scale, 0)
+                                      H, 1, r, s.scale, 0, 0.0, self.sinks)

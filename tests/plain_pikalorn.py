@@ -260,3 +260,12 @@ def forward(config: dict, w: dict, tokens, return_streams: bool = False):
         streams.append(x.copy())
     logits = rms_norm(x, w["final.norm"], eps) @ w["head"].T
     return (logits, np.stack(streams)) if return_streams else logits
+
+
+def greedy(config: dict, w: dict, prompt, n: int):
+    """n tokens chosen greedily (the first largest logit), the whole sequence recomputed for every token."""
+    seq, out = list(prompt), []
+    for _ in range(n):
+        out.append(int(np.argmax(forward(config, w, seq)[-1])))
+        seq.append(out[-1])
+    return out
