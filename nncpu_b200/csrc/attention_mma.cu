@@ -76,7 +76,7 @@ __device__ __forceinline__ float ld_cluster_(const float* local, uint32_t rank) 
 template <int HD>
 __global__ void merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                              __nv_bfloat16* __restrict__ out, int n_heads, int n_kv, int n_splits,
-                             const float* __restrict__ sinks) {
+                             const float* __restrict__ sinks, const float* __restrict__ gate, long gate_ld) {
     const int h = blockIdx.x, t = blockIdx.y, d = threadIdx.x;
     const int G = n_heads / n_kv, kvh = h / G, head = h % G;
     const size_t pb = ((size_t)t * n_kv + kvh) * n_splits;
@@ -90,7 +90,9 @@ __global__ void merge_kernel(const float* __restrict__ part_o, const float* __re
         l = fmaf(part_ml[((pb + s) * G + head) * 2 + 1], c, l);
     }
     if (sinks != nullptr && l > 0.0f) l += exp2f(sinks[h] * kLog2e - m);
-    out[((size_t)t * n_heads + h) * HD + d] = __float2bfloat16_rn(l > 0.0f ? o / l : 0.0f);
+    float res = l > 0.0f ? o / l : 0.0f;
+    if (gate != nullptr) res *= 1.0f / (1.0f + expf(-gate[(size_t)t * gate_ld + (size_t)h * HD + d]));
+    out[((size_t)t * n_heads + h) * HD + d] = __float2bfloat16_rn(res);
 }
 
 // ---------------------------------------------------------------------------
@@ -345,6 +347,9 @@ struct FusedQK {
     float slope_base;         // not of the projections: b != 0 gives head h the distance bias 2^(-b (h + 1) / n_heads) * (pos - key)
     float temp_coef;          // c != 0: the query at position p is multiplied by 1 + c ln(floor((p + 1) / temp_every) + 1)
     int temp_every;
+    int values_are_keys;      // the row holds no v heads: a token's value is its key as projected (before norm and rotation)
+    int gate_at;              // >= 0: the row's heads from gate_at on are logits, one a lane of the output: the output is
+                              // multiplied by their sigmoid; < 0: no gate
 };
 
 // One head's HD float32 values through norm (if gamma) and rotation (if cs) to bfloat16; a warp's job.  A lane holds
@@ -399,7 +404,7 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restri
                    const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ block_table, int bt_stride,
                    const int* __restrict__ tok_seq, const int* __restrict__ tok_pos, __nv_bfloat16* __restrict__ out,
                    float* __restrict__ part_o, float* __restrict__ part_ml, int n_heads, int n_kv, float scale2,
-                   int window, const FusedQK f, const float* __restrict__ sinks) {
+                   int window, const FusedQK f, const float* __restrict__ sinks, int kv_rep) {
     constexpr int kTileBytes = kPage * HD * 2;
     constexpr int kChunks = HD / 8;
     constexpr int W = HD + 2;
@@ -428,7 +433,9 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restri
     const int* table = block_table + (size_t)seq * bt_stride;
 
     auto issue = [&](int page_idx, int stage) {
-        const size_t base = ((size_t)table[page_idx] * n_kv + kvh) * (size_t)(kPage * HD);
+        // kv_rep > 1: more than 16 heads share a key/value head, and kv_rep blocks each serve a part of them from
+        // the same pages (n_kv counts those blocks; the pages hold n_kv / kv_rep heads)
+        const size_t base = ((size_t)table[page_idx] * (n_kv / kv_rep) + kvh / kv_rep) * (size_t)(kPage * HD);
         const uint32_t dst = smem_u32_(dsm) + stage * 2 * kTileBytes;
 #pragma unroll
         for (int i = threadIdx.x; i < kPage * kChunks; i += 128) {
@@ -459,7 +466,8 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restri
             if (warp == 0)
                 finish_head<HD>(row + (size_t)(n_heads + kvh) * HD, f.k_gamma, f.g_dt, f.eps, cs_row, kv_s, lane);
             if (warp == 1)
-                finish_head<HD>(row + (size_t)(n_heads + n_kv + kvh) * HD, nullptr, 0, 0.0f, nullptr, kv_s + HD, lane);
+                finish_head<HD>(row + (size_t)(n_heads + (f.values_are_keys ? 0 : n_kv) + kvh) * HD, nullptr, 0, 0.0f, nullptr,
+                                kv_s + HD, lane);
         }
         __syncthreads();
         if (owner && threadIdx.x < 2 * kChunks) {
@@ -628,7 +636,10 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restri
         }
         if (n_splits == 1) {
             if (sinks != nullptr && ll > 0.0f) ll += exp2f(sinks[kvh * G + head] * kLog2e - mm);
-            out[out_row + i] = __float2bfloat16_rn(ll > 0.0f ? oo / ll : 0.0f);
+            float res = ll > 0.0f ? oo / ll : 0.0f;
+            if (kFused && f.gate_at >= 0)
+                res *= 1.0f / (1.0f + expf(-f.qkv[((size_t)t * f.per_tok + f.gate_at + kvh * G + head) * HD + d]));
+            out[out_row + i] = __float2bfloat16_rn(res);
         } else if (kCluster) {
             merged[head * W + d] = oo;
             if (d == 0) {
@@ -674,7 +685,10 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restri
                 }
             }
             if (sinks != nullptr && ll > 0.0f) ll += exp2f(sinks[kvh * G + head] * kLog2e - mm);
-            out[out_row + i] = __float2bfloat16_rn(ll > 0.0f ? oo / ll : 0.0f);
+            float res = ll > 0.0f ? oo / ll : 0.0f;
+            if (kFused && f.gate_at >= 0)
+                res *= 1.0f / (1.0f + expf(-f.qkv[((size_t)t * f.per_tok + f.gate_at + kvh * G + head) * HD + d]));
+            out[out_row + i] = __float2bfloat16_rn(res);
         }
         cluster_barrier_();   // no block leaves while its result may still be read
     }
@@ -686,7 +700,11 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, const
                   float scale, int window, int n_splits, cudaStream_t stream, const FusedQK* fused = nullptr,
                   float slope_base = 0.0f, const float* sinks = nullptr) {
     using Kernel = void (*)(const __nv_bfloat16*, const __nv_bfloat16*, const __nv_bfloat16*, const int*, int, const int*,
-                            const int*, __nv_bfloat16*, float*, float*, int, int, float, int, const FusedQK, const float*);
+                            const int*, __nv_bfloat16*, float*, float*, int, int, float, int, const FusedQK, const float*, int);
+    // a block serves at most 16 heads of a key/value head: where more share one, kv_rep blocks take a part each
+    int kv_rep = 1;
+    while ((n_heads / n_kv) % kv_rep != 0 || n_heads / n_kv / kv_rep > 16) ++kv_rep;
+    n_kv *= kv_rep;
     const int G = n_heads / n_kv;
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)n_tok * n_kv * n_splits * G * HD : nullptr;
@@ -723,12 +741,14 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, const
     const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages,
                                              (const __nv_bfloat16*)v_pages, block_table, bt_stride, tok_seq, tok_pos,
                                              (__nv_bfloat16*)out, part_o, part_ml, n_heads, n_kv, scale * kLog2e, window, f,
-                                             sinks);
+                                             sinks, kv_rep);
     NN_CHECK(e == cudaSuccess, "attention decode (%d splits%s): launch failed: %s", n_splits, cluster ? ", cluster" : "",
              cudaGetErrorString(e));
     if (n_splits > 1 && !cluster) {
-        merge_kernel<HD><<<dim3(n_heads, n_tok), HD, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, n_heads, n_kv,
-                                                                  n_splits, sinks);
+        const bool gated = fused && fused->gate_at >= 0;
+        merge_kernel<HD><<<dim3(n_heads, n_tok), HD, 0, stream>>>(
+            part_o, part_ml, (__nv_bfloat16*)out, n_heads, n_kv, n_splits, sinks,
+            gated ? f.qkv + (size_t)f.gate_at * HD : nullptr, gated ? (long)f.per_tok * HD : 0l);
         NN_LAUNCH_OK("attention merge");
     }
     return 0;
@@ -758,7 +778,7 @@ int launch_prefill(const void* q, const void* k_pages, const void* v_pages, cons
 
 // Whether the tensor-core attention kernels take these sizes (bfloat16 q, cache and output assumed).
 extern "C" int nncpu_attention_mma_supported(int n_heads, int n_kv, int hd) {
-    return (hd == 64 || hd == 128) && n_kv > 0 && n_heads % n_kv == 0 && n_heads / n_kv <= 16;
+    return (hd == 64 || hd == 128) && n_kv > 0 && n_heads % n_kv == 0;
 }
 
 // Floats of scratch the decode kernel needs for n_tok tokens cut into n_splits splits (0 for one split).
@@ -777,7 +797,7 @@ extern "C" int nncpu_attention_decode_mma(const void* q, const void* k_pages, co
                                           int n_splits, float slope_base, const float* sinks, void* stream) {
     NN_CHECK(nncpu_attention_mma_supported(n_heads, n_kv, hd),
              "attention (tensor cores): %d heads over %d key/value heads of size %d is not supported "
-             "(head size 64 or 128, at most 16 heads per key/value head)", n_heads, n_kv, hd);
+             "(head size 64 or 128, heads a multiple of key/value heads)", n_heads, n_kv, hd);
     NN_CHECK(n_tok >= 0 && n_splits >= 1 && n_splits <= 65535, "attention decode: %d tokens, %d splits",
              n_tok, n_splits);
     if (scratch == nullptr && n_splits > 1)
@@ -805,12 +825,15 @@ extern "C" int nncpu_attention_decode_mma_from_qkv(const float* qkv, const void*
                                                    const int* tok_seq, const int* tok_pos, void* out, float* scratch,
                                                    long scratch_floats, int n_tok, int n_heads, int n_kv, int hd,
                                                    float scale, int window, int n_splits, float slope_base,
-                                                   float temp_coef, int temp_every, void* stream) {
+                                                   float temp_coef, int temp_every, const float* sinks,
+                                                   int values_are_keys, int gated, void* stream) {
     NN_CHECK(nncpu_attention_mma_supported(n_heads, n_kv, hd),
              "attention (tensor cores): %d heads over %d key/value heads of size %d is not supported "
-             "(head size 64 or 128, at most 16 heads per key/value head)", n_heads, n_kv, hd);
+             "(head size 64 or 128, heads a multiple of key/value heads)", n_heads, n_kv, hd);
     NN_CHECK(n_tok >= 0 && n_splits >= 1 && n_splits <= 65535, "attention decode: %d tokens, %d splits",
              n_tok, n_splits);
+    NN_CHECK(n_heads / n_kv <= 16, "attention decode (from projections): %d heads share a key/value head (at most 16)",
+             n_heads / n_kv);
     NN_CHECK(qkv != nullptr && ((uintptr_t)qkv % 16) == 0 && ((uintptr_t)cos_sin % 8) == 0 && ((uintptr_t)k_pages % 16) == 0 &&
                  ((uintptr_t)v_pages % 16) == 0,
              "attention decode (from projections): the projections and the cache must be 16-byte aligned, the rotation "
@@ -824,7 +847,12 @@ extern "C" int nncpu_attention_decode_mma_from_qkv(const float* qkv, const void*
     if (n_tok == 0) return 0;
     FusedQK f{};
     f.qkv = qkv;
-    f.per_tok = append ? n_heads + 2 * n_kv : n_heads;
+    // a token's row: the heads of q, then (if appended here) of k and, unless the values are the keys, of v, then
+    // (if gated) as many heads of gate logits as of q
+    const int kv_heads_in_row = append ? (values_are_keys ? n_kv : 2 * n_kv) : 0;
+    f.per_tok = n_heads + kv_heads_in_row + (gated ? n_heads : 0);
+    f.values_are_keys = values_are_keys;
+    f.gate_at = gated ? n_heads + kv_heads_in_row : -1;
     f.q_gamma = q_gamma; f.k_gamma = k_gamma; f.g_dt = g_dt; f.eps = eps;
     f.cs = (const float2*)cos_sin;
     f.k_pages = append ? (__nv_bfloat16*)k_pages : nullptr;
@@ -835,9 +863,9 @@ extern "C" int nncpu_attention_decode_mma_from_qkv(const float* qkv, const void*
     f.temp_every = temp_every;
     if (hd == 64)
         return launch_decode<64>(nullptr, k_pages, v_pages, block_table, bt_stride, tok_seq, tok_pos, out, scratch, n_tok,
-                                 n_heads, n_kv, scale, window, n_splits, (cudaStream_t)stream, &f);
+                                 n_heads, n_kv, scale, window, n_splits, (cudaStream_t)stream, &f, 0.0f, sinks);
     return launch_decode<128>(nullptr, k_pages, v_pages, block_table, bt_stride, tok_seq, tok_pos, out, scratch, n_tok,
-                              n_heads, n_kv, scale, window, n_splits, (cudaStream_t)stream, &f);
+                              n_heads, n_kv, scale, window, n_splits, (cudaStream_t)stream, &f, 0.0f, sinks);
 }
 
 // Any mix of new tokens per sequence: sequence b brings the flat tokens cu_seqlens[b] .. cu_seqlens[b + 1] - 1
@@ -849,7 +877,7 @@ extern "C" int nncpu_attention_prefill_mma(const void* q, const void* k_pages, c
                                            void* stream) {
     NN_CHECK(nncpu_attention_mma_supported(n_heads, n_kv, hd),
              "attention (tensor cores): %d heads over %d key/value heads of size %d is not supported "
-             "(head size 64 or 128, at most 16 heads per key/value head)", n_heads, n_kv, hd);
+             "(head size 64 or 128, heads a multiple of key/value heads)", n_heads, n_kv, hd);
     NN_CHECK(n_tok >= 0 && n_seqs >= 0, "attention prefill: %d tokens of %d sequences", n_tok, n_seqs);
     if (n_tok == 0 || n_seqs == 0) return 0;
     if (hd == 64)
@@ -925,7 +953,7 @@ extern "C" int nncpu_attention_decode_mma_static(const void* q, const void* k_pa
                                                  int hd, float scale, int window, int n_splits, void* stream) {
     NN_CHECK(nncpu_attention_mma_supported(n_heads, n_kv, hd),
              "attention (tensor cores): %d heads over %d key/value heads of size %d is not supported "
-             "(head size 64 or 128, at most 16 heads per key/value head)", n_heads, n_kv, hd);
+             "(head size 64 or 128, heads a multiple of key/value heads)", n_heads, n_kv, hd);
     NN_CHECK(n_tok >= 0 && n_splits >= 1 && n_splits <= 65535, "attention decode (static scratch): %d tokens, %d splits", n_tok,
              n_splits);
     const long need = nncpu_attention_decode_scratch_floats(n_tok, n_heads, n_kv, hd, n_splits);

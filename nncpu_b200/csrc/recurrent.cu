@@ -486,13 +486,18 @@ extern "C" int nncpu_delta_prepare(const float* proj, int ld, const void* conv_w
 __device__ __forceinline__ void cp_async4(void* dst, const void* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
+__device__ __forceinline__ void cp_async16_(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit_() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_one_() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
 
 // The recurrence over the step's tokens, sequence by sequence in order.  The columns of S do not depend on one
 // another.  A block of four warps owns 4 * 32 / R columns of one head's state for one sequence; R lanes share a column,
-// lane r of them keeping the rows r + R ii (ii < DR) in registers, so that S^T k costs DR multiply-adds and log2(R)
-// shuffles a token, the only exchange on the chain from token to token (the sum for o is off that chain).  k, q, v,
+// lane r of them keeping DR rows in registers (the groups of four rows 4 (c R + r) .. + 3, c < DR / 4: the R lanes of
+// a column read R neighbouring 16-byte pieces of k and of q from shared memory with one load), so that S^T k costs DR
+// multiply-adds and log2(R) shuffles a token, the only exchange on the chain from token to token (the sum for o is
+// off that chain).  k, q, v,
 // g and beta of a group of tokens are staged in shared memory by asynchronous copies, the next group's in flight under
 // this group's arithmetic.  The order of operations of a (sequence, head, column) does not depend on how the sequence
 // was cut into steps or on what else the step holds.  A negative slot (padding): zeros out, no state touched.
@@ -501,18 +506,21 @@ __global__ void __launch_bounds__(128)
 delta_scan_kernel(const float* __restrict__ xc, const float* __restrict__ gb, float* __restrict__ state,
                   long slot_stride, const int* __restrict__ seq_slots, const int* __restrict__ cu_seqlens, float* __restrict__ o, int H,
                   int G, int d, int e) {
+    static_assert(DR % 4 == 0, "a lane keeps whole groups of four rows");
     constexpr int DP = DR * R;                      // rows the lanes cover (>= d; the rest hold zeros)
     constexpr int CW = 32 / R;                      // columns a warp
     constexpr int COLS = 4 * CW;                    // columns a block
     constexpr int TB = DP <= 256 ? 8 : (DP <= 512 ? 4 : 2);       // tokens a group
     constexpr int BUF = TB * (2 * DP + COLS + 2);   // floats a buffer: k, q [TB][DP], v [TB][COLS], (g, beta) [TB]
-    extern __shared__ float dsm_[];
+    extern __shared__ __align__(16) float dsm_[];
     const int seq = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31, r = lane % R;
+    auto row_of = [&](int ii) { return ((ii >> 2) * R + r) * 4 + (ii & 3); };      // the row that S[ii] holds
     const int col_local = warp * CW + lane / R, col0 = blockIdx.z * COLS, col = col0 + col_local;
     const int t0 = cu_seqlens[seq], t1 = cu_seqlens[seq + 1];
     const int slot = seq_slots[seq];
     const int C = 2 * G * d + H * e;
+    const bool wide = (d & 3) == 0 && (C & 3) == 0 && (reinterpret_cast<uintptr_t>(xc) & 15) == 0;
     if (slot < 0) {
         if (r == 0 && col < e)
             for (int t = t0; t < t1; ++t) o[(size_t)t * H * e + (size_t)h * e + col] = 0.0f;
@@ -524,7 +532,7 @@ delta_scan_kernel(const float* __restrict__ xc, const float* __restrict__ gb, fl
     float S[DR];
 #pragma unroll
     for (int ii = 0; ii < DR; ++ii) {
-        const int i = r + R * ii;
+        const int i = row_of(ii);
         S[ii] = (i < d && col < e) ? s_head[(size_t)i * e + col] : 0.0f;
     }
     for (int i = tid; i < 2 * BUF; i += 128) dsm_[i] = 0.0f;      // rows beyond d and columns beyond e stay zero
@@ -535,11 +543,21 @@ delta_scan_kernel(const float* __restrict__ xc, const float* __restrict__ gb, fl
         float* qb = kb + TB * DP;
         float* vb = qb + TB * DP;
         float* gbb = vb + TB * COLS;
-        for (int idx = tid; idx < nt * d; idx += 128) {
-            const int tt = idx / d, i = idx % d;
-            const float* src = xc + (size_t)(g0 + tt) * C;
-            cp_async4(kb + tt * DP + i, src + k_at + i);
-            cp_async4(qb + tt * DP + i, src + q_at + i);
+        if (wide) {          // rows of xc start on 16-byte borders, and so do the heads in them
+            const int d4 = d >> 2;
+            for (int idx = tid; idx < nt * d4; idx += 128) {
+                const int tt = idx / d4, i = (idx % d4) << 2;
+                const float* src = xc + (size_t)(g0 + tt) * C;
+                cp_async16_(kb + tt * DP + i, src + k_at + i);
+                cp_async16_(qb + tt * DP + i, src + q_at + i);
+            }
+        } else {
+            for (int idx = tid; idx < nt * d; idx += 128) {
+                const int tt = idx / d, i = idx % d;
+                const float* src = xc + (size_t)(g0 + tt) * C;
+                cp_async4(kb + tt * DP + i, src + k_at + i);
+                cp_async4(qb + tt * DP + i, src + q_at + i);
+            }
         }
         for (int idx = tid; idx < nt * COLS; idx += 128) {
             const int tt = idx / COLS, c = idx % COLS;
@@ -563,14 +581,18 @@ delta_scan_kernel(const float* __restrict__ xc, const float* __restrict__ gb, fl
         const float* qb = kb + TB * DP;
         const float* vb = qb + TB * DP;
         const float* gbb = vb + TB * COLS;
-        for (int tt = 0; tt < nt; ++tt) {
+        // One token: the chain from token to token is S^T k (DR multiply-adds in four sums, log2(R) shuffles), u, and
+        // the update of S.  The lane's part of o = S^T q is returned; its sum over the lanes is off the chain.
+        auto token = [&](int tt) -> float {
             const float g = gbb[tt * 2], beta = gbb[tt * 2 + 1], v = vb[tt * COLS + col_local];
             float kk[DR];
             float p[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-            for (int ii = 0; ii < DR; ++ii) {
-                kk[ii] = kb[tt * DP + r + R * ii];
-                p[ii & 3] = fmaf(kk[ii], S[ii], p[ii & 3]);
+            for (int c = 0; c < DR / 4; ++c) {
+                const float4 k4 = *reinterpret_cast<const float4*>(kb + tt * DP + (c * R + r) * 4);
+                kk[4 * c] = k4.x; kk[4 * c + 1] = k4.y; kk[4 * c + 2] = k4.z; kk[4 * c + 3] = k4.w;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) p[j] = fmaf(kk[4 * c + j], S[4 * c + j], p[j]);
             }
             float ks = (p[0] + p[1]) + (p[2] + p[3]);
 #pragma unroll
@@ -578,20 +600,45 @@ delta_scan_kernel(const float* __restrict__ xc, const float* __restrict__ gb, fl
             const float u = beta * (v - g * ks);       // S^T k of the decayed state is g times that of the old one
             float a[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-            for (int ii = 0; ii < DR; ++ii) {
-                S[ii] = fmaf(g, S[ii], kk[ii] * u);
-                a[ii & 3] = fmaf(qb[tt * DP + r + R * ii], S[ii], a[ii & 3]);
-            }
-            float os = (a[0] + a[1]) + (a[2] + a[3]);
+            for (int c = 0; c < DR / 4; ++c) {
+                const float4 q4 = *reinterpret_cast<const float4*>(qb + tt * DP + (c * R + r) * 4);
+                const float qq[4] = {q4.x, q4.y, q4.z, q4.w};
 #pragma unroll
-            for (int m = 1; m < R; m <<= 1) os += __shfl_xor_sync(0xffffffffu, os, m);
-            if (r == 0 && col < e) o[(size_t)(g0 + tt) * H * e + (size_t)h * e + col] = os;
+                for (int j = 0; j < 4; ++j) {
+                    S[4 * c + j] = fmaf(g, S[4 * c + j], kk[4 * c + j] * u);
+                    a[j] = fmaf(qq[j], S[4 * c + j], a[j]);
+                }
+            }
+            return (a[0] + a[1]) + (a[2] + a[3]);
+        };
+        if (nt == TB) {
+            // a whole group, unrolled: the next token's loads issue under this token's chain, and the sums for o of
+            // all its tokens are added over the lanes together, as independent chains (the same additions in the same
+            // order as one by one)
+            float os[TB];
+#pragma unroll
+            for (int tt = 0; tt < TB; ++tt) os[tt] = token(tt);
+#pragma unroll
+            for (int m = 1; m < R; m <<= 1)
+#pragma unroll
+                for (int tt = 0; tt < TB; ++tt) os[tt] += __shfl_xor_sync(0xffffffffu, os[tt], m);
+            if (r == 0 && col < e) {
+#pragma unroll
+                for (int tt = 0; tt < TB; ++tt) o[(size_t)(g0 + tt) * H * e + (size_t)h * e + col] = os[tt];
+            }
+        } else {
+            for (int tt = 0; tt < nt; ++tt) {
+                float os = token(tt);
+#pragma unroll
+                for (int m = 1; m < R; m <<= 1) os += __shfl_xor_sync(0xffffffffu, os, m);
+                if (r == 0 && col < e) o[(size_t)(g0 + tt) * H * e + (size_t)h * e + col] = os;
+            }
         }
         __syncthreads();             // the buffer is free for the group after next
     }
 #pragma unroll
     for (int ii = 0; ii < DR; ++ii) {
-        const int i = r + R * ii;
+        const int i = row_of(ii);
         if (i < d && col < e) s_head[(size_t)i * e + col] = S[ii];
     }
 }
@@ -607,6 +654,11 @@ static int launch_delta_scan(const float* xc, const float* gb, float* state, lon
     return 0;
 }
 
+// Blocks of one sequence that the choice of lanes a column aims for: two thirds of the SMs of a 148-SM part.
+constexpr long kDeltaBlocksWanted = 96;
+static int g_delta_lanes = 0;    // a measurement's override of the lanes a column (0: the rule below)
+extern "C" void nncpu_delta_scan_force_lanes(int lanes) { g_delta_lanes = lanes; }
+
 extern "C" int nncpu_delta_scan(const float* xc, const float* gb, float* state, long slot_stride, const int* seq_slots,
                                 const int* cu_seqlens, float* o, int n_seqs, int H, int G, int d, int e, void* stream) {
     NN_CHECK(n_seqs >= 0 && H > 0 && G > 0 && H % G == 0 && d > 0 && e > 0, "delta scan: %d sequences, %d heads of %d x %d",
@@ -615,12 +667,28 @@ extern "C" int nncpu_delta_scan(const float* xc, const float* gb, float* state, 
     NN_CHECK(H <= 65535 && e <= 65535 * 16, "delta scan: grid");
     if (n_seqs == 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
-    if (d <= 32) launch_delta_scan<8, 4>(xc, gb, state, slot_stride, seq_slots, cu_seqlens, o, n_seqs, H, G, d, e, st);
-    else if (d <= 64) launch_delta_scan<16, 4>(xc, gb, state, slot_stride, seq_slots, cu_seqlens, o, n_seqs, H, G, d, e, st);
-    else if (d <= 128) launch_delta_scan<32, 4>(xc, gb, state, slot_stride, seq_slots, cu_seqlens, o, n_seqs, H, G, d, e, st);
-    else if (d <= 256) launch_delta_scan<32, 8>(xc, gb, state, slot_stride, seq_slots, cu_seqlens, o, n_seqs, H, G, d, e, st);
-    else if (d <= 512) launch_delta_scan<32, 16>(xc, gb, state, slot_stride, seq_slots, cu_seqlens, o, n_seqs, H, G, d, e, st);
-    else launch_delta_scan<32, 32>(xc, gb, state, slot_stride, seq_slots, cu_seqlens, o, n_seqs, H, G, d, e, st);
+    // R lanes share a column (R * DR rows cover d).  Few lanes a column mean few shuffles and few warps; a sequence alone
+    // in a step (a prompt) then leaves most of the GPU idle while every warp walks a chain of dependent instructions
+    // a token.  So R grows until ONE sequence's blocks cover most of the SMs (measured: 2 048 tokens of one sequence,
+    // 16 heads of 128 x 128: 577 us with 4 lanes, 464 with 8; 64 sequences of one token: 48 against 54).  R follows
+    // from the layer's sizes alone, never from the step: with R the order in which a column's products are added
+    // changes, and a sequence's numbers must not depend on what else the step holds.
+    const int DP = d <= 32 ? 32 : d <= 64 ? 64 : d <= 128 ? 128 : d <= 256 ? 256 : d <= 512 ? 512 : 1024;
+    int R = DP / 32 < 4 ? 4 : DP / 32;
+    if (g_delta_lanes >= R && g_delta_lanes <= 32 && g_delta_lanes <= DP / 4 && (g_delta_lanes & (g_delta_lanes - 1)) == 0)
+        R = g_delta_lanes;
+    else
+        while (R < 32 && R * 2 <= DP / 4 && (long)H * ((e + 128 / R - 1) / (128 / R)) < kDeltaBlocksWanted) R *= 2;
+#define NN_DELTA(DP_, R_)                                                                                              \
+    if (DP == DP_ && R == R_)                                                                                          \
+        launch_delta_scan<DP_ / R_, R_>(xc, gb, state, slot_stride, seq_slots, cu_seqlens, o, n_seqs, H, G, d, e, st);
+    NN_DELTA(32, 4) NN_DELTA(32, 8)
+    NN_DELTA(64, 4) NN_DELTA(64, 8) NN_DELTA(64, 16)
+    NN_DELTA(128, 4) NN_DELTA(128, 8) NN_DELTA(128, 16) NN_DELTA(128, 32)
+    NN_DELTA(256, 8) NN_DELTA(256, 16) NN_DELTA(256, 32)
+    NN_DELTA(512, 16) NN_DELTA(512, 32)
+    NN_DELTA(1024, 32)
+#undef NN_DELTA
     NN_LAUNCH_OK("delta scan");
     return 0;
 }

@@ -411,8 +411,9 @@ def attention(q, k_pages, v_pages, block_table, tok_seq, tok_pos, out, n_heads: 
 
 def attention_mma_supported(n_heads: int, n_kv: int, head_dim: int, *tensors) -> bool:
     """The tensor-core attention kernels take bfloat16 q, cache and output with
-    head size 64 or 128 and at most 16 query heads per key/value head."""
-    return (head_dim in (64, 128) and n_kv > 0 and n_heads % n_kv == 0 and n_heads // n_kv <= 16
+    head size 64 or 128 (where more than 16 query heads share a key/value head, several blocks of the decode
+    kernel take a part of them each)."""
+    return (head_dim in (64, 128) and n_kv > 0 and n_heads % n_kv == 0
             and all(t.dtype == torch.bfloat16 for t in tensors))
 
 
@@ -458,14 +459,18 @@ def attention_decode_mma(q, k_pages, v_pages, block_table, tok_seq, tok_pos, out
 
 def attention_decode_mma_from_qkv(qkv, q_gamma, k_gamma, eps, cos_sin, k_pages, v_pages, append: bool, block_table,
                                   tok_seq, tok_pos, out, scratch, n_heads: int, n_kv: int, head_dim: int, scale: float,
-                                  window: int, n_splits: int, slope_base: float = 0.0, q_temp=None) -> None:
+                                  window: int, n_splits: int, slope_base: float = 0.0, q_temp=None, sinks=None,
+                                  values_are_keys: bool = False, gated: bool = False) -> None:
     """Decode attention that starts from the float32 projections ``qkv`` [n, per_tok * head_dim] (q heads, then with
     ``append`` the k and v heads): every block makes its queries itself (per-head norm, rotation by ``cos_sin``
     [n, head_dim / 2, 2]), and with ``append`` the token's key and value are made, written to the cache and used.
     One launch in place of ``qk_norm_rope_append`` and ``attention_decode_mma``, with the same arithmetic;
-    ``slope_base`` and ``q_temp`` as there."""
+    ``slope_base``, ``q_temp`` and ``sinks`` as there.  ``values_are_keys``: the rows hold no v heads, a token's value
+    is its key as projected.  ``gated``: n_heads more heads of logits end the rows, and the output is multiplied lane by
+    lane by their sigmoid (in place of ``sigmoid_gate``)."""
     n = out.shape[0]
-    per_tok = n_heads + 2 * n_kv if append else n_heads
+    per_tok = n_heads + (((1 if values_are_keys else 2) * n_kv) if append else 0) + (n_heads if gated else 0)
+    assert sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == n_heads)
     assert qkv.dtype == torch.float32 and qkv.shape == (n, per_tok * head_dim) and qkv.is_contiguous()
     assert out.shape == (n, n_heads * head_dim) and out.dtype == torch.bfloat16
     assert k_pages.dtype == v_pages.dtype == torch.bfloat16 and k_pages.is_contiguous() and v_pages.is_contiguous()
@@ -477,7 +482,8 @@ def attention_decode_mma_from_qkv(qkv, q_gamma, k_gamma, eps, cos_sin, k_pages, 
           _f(eps), _ptr(cos_sin), _ptr(k_pages), _ptr(v_pages), _i(append), _ptr(block_table), _i(block_table.shape[1]),
           _ptr(tok_seq), _ptr(tok_pos), _ptr(out), _ptr(scratch), ctypes.c_long(0 if scratch is None else scratch.numel()),
           _i(n), _i(n_heads), _i(n_kv), _i(head_dim), _f(scale), _i(window), _i(n_splits), _f(slope_base),
-          _f(q_temp[0] if q_temp else 0.0), _i(q_temp[1] if q_temp else 1), _stream())
+          _f(q_temp[0] if q_temp else 0.0), _i(q_temp[1] if q_temp else 1), _ptr(sinks), _i(values_are_keys), _i(gated),
+          _stream())
 
 
 def attention_prefill_mma(q, k_pages, v_pages, block_table, cu_seqlens, tok_pos, out, n_seqs: int, n_heads: int,

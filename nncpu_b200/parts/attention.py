@@ -165,13 +165,16 @@ class Attention(Mixer):
             with rt.phase("attn_rope"):
                 cos_sin = None if self.position is None else self.position.tables(ctx)
             if self._decode_from_projections(ctx, cache):
-                # a decode step: norm, rotation and append are the attention kernel's own first steps
+                # a decode step: norm, rotation and append are the attention kernel's own first steps, the sink's term
+                # and the output gate its last
                 with self._core_phase(ctx, cache):
                     n_splits, scratch = self._decode_splits(ctx)
                     ops.attention_decode_mma_from_qkv(qkv, self.q_gamma, self.k_gamma, eps, cos_sin, cache.k_pages,
                                                       cache.v_pages, not self.shared_kv, cache.block_table, ctx.tok_seq,
                                                       ctx.tok_pos, attn, scratch, s.n_heads, s.n_kv_heads, s.head_dim,
-                                                      s.scale, self.span, n_splits, s.slope_base, self.q_temp)
+                                                      s.scale, self.span, n_splits, s.slope_base, self.q_temp,
+                                                      sinks=self.sinks, values_are_keys=s.values_are_keys,
+                                                      gated=s.out_gate)
             else:
                 q = rt.empty(n, self.q_size)
                 with rt.phase("attn_rope"):
@@ -181,9 +184,9 @@ class Attention(Mixer):
                                             values_are_keys=s.values_are_keys)
                 with self._core_phase(ctx, cache):
                     self._attend(ctx, q, cache, attn)
-            if s.out_gate:
-                with rt.phase("attn_gate"):
-                    ops.sigmoid_gate(attn, qkv, self.gate_col)
+                if s.out_gate:      # (the decode kernel that starts from the projections applies the gate itself)
+                    with rt.phase("attn_gate"):
+                        ops.sigmoid_gate(attn, qkv, self.gate_col)
         with rt.phase("attn_out", self.w_o, n):
             # the last write into the residual stream: it may leave the next norm its input
             rt.linear(attn, self.w_o, self.b_o, residual, accumulate=not getattr(ctx, "branch_is_fresh", False),
@@ -203,10 +206,9 @@ class Attention(Mixer):
         """Whether this step's attention can start from the float32 projections: a decode step on the tensor-core
         kernel, every lane of a head rotated (or none), norm weights of one type."""
         s = self.spec
-        if s.values_are_keys or s.out_gate or s.sink:
-            return False
         return (not self.plain_core and ctx.is_decode and self.rt.dtype == torch.bfloat16 and cache.k_pages.dtype == torch.bfloat16
                 and ops.attention_mma_supported(s.n_heads, s.n_kv_heads, s.head_dim)
+                and s.n_heads // s.n_kv_heads <= 16
                 and (self.position is None or self.position.half * 2 == s.head_dim)
                 and (self.q_gamma is None or self.k_gamma is None or self.q_gamma.dtype == self.k_gamma.dtype))
 

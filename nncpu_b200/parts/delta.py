@@ -14,8 +14,8 @@ before the sequence's start):
 The six projections of h are one product (their rows stacked); it runs in the run's element type with 32-bit
 accumulators and its results stay float32.  Convolutions, activations, unit vectors, decays, the recurrence and the
 norm are 32-bit in both run types.  The recurrence walks a sequence's tokens in order with a fixed order of operations
-per (sequence, head, column), so a prompt cut into portions, a batch of unequal sequences and a prompt decoded token by
-token give the same bits.
+per (sequence, head, column) that follows from the layer's sizes alone, so a prompt cut into portions, a batch of
+unequal sequences and a prompt decoded token by token give the same bits.
 """
 from __future__ import annotations
 

@@ -188,7 +188,8 @@ def test_softmax_with_a_sink_alone(dtype, nh, nkv, hd):
     assert float(out[:, :hd].float().abs().max()) < 0.2 * float(none[:, :hd].float().abs().max()), "a sink far above them"
 
 
-@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 64), (2, 1, 128), (16, 1, 64), (12, 4, 128), (5, 5, 64), (1, 1, 64), (9, 1, 128)])
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 64), (2, 1, 128), (16, 1, 64), (12, 4, 128), (5, 5, 64), (1, 1, 64), (9, 1, 128),
+                                       (32, 1, 128), (40, 2, 64), (17, 1, 64)])
 def test_softmax_with_a_sink_on_the_tensor_core_kernels(nh, nkv, hd):
     """The bfloat16 kernels for prompts (mma.sync tiles, tcgen05 tiles) and for decode steps (one split; several merged
     inside a cluster; several merged through scratch) with sinks: one far above the scores, one far below, ordinary ones.
@@ -262,6 +263,46 @@ def test_values_that_are_the_keys_and_the_gate_on_the_heads():
     got = heads.to(DEV)
     ops.sigmoid_gate(got, qkv.to(DEV), (nh + nkv) * hd)
     check(got, heads.double().numpy() * P.sigmoid(x[:, (nh + nkv) * hd:(nh + nkv + nh) * hd]), 1e-6, "gated heads")
+
+
+@pytest.mark.parametrize("nh,nkv,hd,n_splits,with_scratch", [(4, 2, 64, 1, False), (8, 2, 128, 3, False), (16, 1, 64, 2, True),
+                                                             (6, 6, 128, 5, True), (3, 1, 64, 2, False)])
+def test_decode_step_from_the_projections_with_sinks_own_values_and_the_gate(nh, nkv, hd, n_splits, with_scratch):
+    """One token each of three sequences (at positions 0, 64 and 299: the first key of a sequence, the first of a page,
+    far into a sequence) through the decode kernel that starts from the 32-bit projections: per-head norms, rotation,
+    the append of the key and of the key as projected as the value, softmax with sinks, and the sigmoid gate, against
+    the plain statement of every one of them; then the pages must hold what the separate append kernel writes."""
+    lens = [1, 65, 300]
+    g = torch.Generator().manual_seed(nh * hd + n_splits)
+    kp, vp, table, ks, vs = scatter_pages(12, nkv, hd, lens, torch.bfloat16, seed=6)
+    sinks = torch.randn(nh, generator=g) + 1.0
+    qg, kg = torch.randn(hd, generator=g) + 1, torch.randn(hd, generator=g) + 1
+    r = rot(10000.0, hd)
+    pos = [l - 1 for l in lens]
+    qkv = torch.randn(3, (nh + nkv + nh) * hd, generator=g)
+    x = qkv.double().numpy()
+    f, _ = P.rotary_frequencies(r)
+    cs = torch.tensor(np.stack([np.cos(np.outer(pos, f)), np.sin(np.outer(pos, f))], axis=-1), dtype=torch.float32, device=DEV)
+    q = P.rotate(P.rms_norm(x[:, :nh * hd].reshape(3, nh, hd), qg.double().numpy(), 1e-5), pos, r, "half")
+    k_raw = x[:, nh * hd:(nh + nkv) * hd].reshape(3, nkv, hd)
+    k_new = P.rotate(P.rms_norm(k_raw, kg.double().numpy(), 1e-5), pos, r, "half")
+    gate = P.sigmoid(x[:, (nh + nkv) * hd:])
+    want = []
+    for b in range(3):
+        kb, vb = ks[b].double().numpy().copy(), vs[b].double().numpy().copy()
+        kb[-1], vb[-1] = k_new[b], k_raw[b]                 # the token's own key and value replace the last stored ones
+        want.append(plain_sink_attention(q[b:b + 1], kb, vb, [pos[b]], 0.2, sinks.double().numpy()).reshape(-1) * gate[b])
+    seq, dpos = i32([0, 1, 2]), i32(pos)
+    scratch = torch.empty(ops.attention_decode_scratch_floats(3, nh, nkv, hd, n_splits), device=DEV) if with_scratch else None
+    got = torch.empty(3, nh * hd, dtype=torch.bfloat16, device=DEV)
+    kp2, vp2 = kp.clone(), vp.clone()
+    ops.attention_decode_mma_from_qkv(qkv.to(DEV), qg.to(DEV), kg.to(DEV), 1e-5, cs, kp, vp, True, table, seq, dpos, got, scratch,
+                                      nh, nkv, hd, 0.2, 0, n_splits, sinks=sinks.to(DEV), values_are_keys=True, gated=True)
+    check(got, np.stack(want), 2e-2, "decode from the projections")
+    q_out = torch.empty(3, nh * hd, dtype=torch.bfloat16, device=DEV)
+    ops.qk_norm_rope_append(qkv.to(DEV), qg.to(DEV), kg.to(DEV), 1e-5, cs, seq, dpos, table, kp2, vp2, q_out, nh, nkv, hd,
+                            values_are_keys=True)
+    assert torch.equal(kp, kp2) and torch.equal(vp, vp2), "the pages differ from the separate append kernel's"
 
 
 @pytest.mark.parametrize("r,R,qr", [(36, 6, 30), (64, 64, 96), (998, 2, 3), (12, 8, 20)])
