@@ -801,3 +801,81 @@ def test_trace_replay_of_many_short_requests(folders, tmp_path):
         got = np.fromfile(out / f"{n}.f32", dtype="<f4").reshape(-1, V)
         ref = np.concatenate([want[k][pos] for k, pos in rows])
         check(got, ref, 1e-4, f"step {n}")
+
+
+def random_pikalorn(rs):
+    """A random configuration: any order of the three kinds of layer, head sizes in and out of what the tensor-core
+    kernels take, any grouping of heads, layers that read an earlier latent layer's cache, some without a feed-forward."""
+    width = int(rs.choice([72, 100, 136, 200, 256]))
+    layers, owners = [], []
+    for i in range(int(rs.randint(2, 7))):
+        kind = rs.choice(["attention", "latent_attention", "delta"])
+        mlp = dense(int(rs.choice([40, 88, 136, 264]))) if rs.rand() < 0.8 else None
+        if kind == "attention":
+            kv, group, dim = int(rs.choice([1, 2, 3])), int(rs.choice([1, 2, 4, 5])), int(rs.choice([16, 24, 48, 64, 128]))
+            dims = int(rs.choice([dim, dim // 2, 2]))
+            layers.append(att(kv * group, kv, dim, float(rs.choice([dim ** -0.5, 0.2])), rot(float(rs.choice([1e4, 1e6, 300.0])), dims - dims % 2 or 2), mlp=mlp))
+        elif kind == "latent_attention":
+            if owners and rs.rand() < 0.5:
+                j = int(rs.choice(owners))
+                m = layers[j]["mixer"]
+                layers.append(lat(int(rs.choice([1, 2, 3, 8])), int(rs.choice([8, 16, 32, 64])), m["rot_dim"], int(rs.choice([8, 20, 64])),
+                                  m["kv_rank"], int(rs.choice([12, 64, 100])), float(rs.choice([0.1, 0.25])), m["rot"], kv_from=j, mlp=mlp))
+            else:
+                R = int(rs.choice([2, 8, 32, 64]))
+                rank = int(rs.choice([24, 32, 64, 96, 128 - R]))
+                sc = None if rs.rand() < 0.3 else (float(rs.choice([2.0, 4.0, 16.0])), float(rs.choice([32, 256, 1024])),
+                                                   float(rs.choice([8.0, 32.0])), float(rs.choice([0.5, 1.0, 2.0])))
+                owners.append(i)
+                layers.append(lat(int(rs.choice([1, 2, 4, 6])), int(rs.choice([8, 16, 32, 64])), R, int(rs.choice([8, 20, 64])), rank,
+                                  int(rs.choice([12, 64, 100])), float(rs.choice([0.1, 0.25])), rot(float(rs.choice([1e4, 500.0])), R, sc), mlp=mlp))
+        else:
+            kv, group = int(rs.choice([1, 2, 3])), int(rs.choice([1, 2, 3]))
+            layers.append(dlt(kv * group, kv, int(rs.choice([8, 20, 64, 128, 136])), int(rs.choice([8, 20, 64, 128])), int(rs.choice([1, 2, 4, 5])), mlp=mlp))
+    cfg = {"architecture": "Pikalorn", "vocab": int(rs.randint(100, 600)), "width": width,
+           "norm": {"eps": float(rs.choice([1e-6, 1e-5]))}, "layers": layers}
+    if rs.rand() < 0.7:
+        cfg["embedding"] = {"scale": float(rs.choice([1.0, 3.0, width ** 0.5]))}
+    return cfg
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("seed", range(8))
+def test_random_configuration_and_trace(tmp_path, seed, dtype):
+    """Random configurations, each with a batch of unequal prompts (the first one cut in two steps the second time
+    round), decoding with early leavers, then the same again on the slots, pages and state rows given back."""
+    rs = np.random.RandomState(4000 + seed)
+    cfg = random_pikalorn(rs)
+    folder = write_folder(tmp_path / "m", cfg, seed, STORE[dtype], sharpen=2.0)
+    model = Model.load(folder, dtype=dtype)
+    lens = [int(rs.choice([1, 2, 17, 40, 65, 130, 260])) for _ in range(int(rs.choice([1, 2, 3, 4])))]
+    if rs.rand() < 0.4:
+        lens[0] = int(rs.choice([300, 520]))
+    n_decode = [int(rs.randint(0, 10)) for _ in lens]
+    reqs = [rs.randint(0, cfg["vocab"], size=n + d).tolist() for n, d in zip(lens, n_decode)]
+    want = [plain_logits(folder, r) for r in reqs]
+    engine = Engine(model, max_tokens=64 * (sum((len(r) + 63) // 64 for r in reqs) + 2))
+    for round_ in range(2):
+        slots = [engine.alloc_slot() for _ in reqs]
+        rows = [Rows(dtype, f"seed {seed} round {round_} request {b}") for b in range(len(reqs))]
+        cut = lens[0] // 2 if lens[0] > 40 and round_ == 1 else 0
+        if cut:
+            engine.step(slots[:1], [reqs[0][:cut]], [[]])
+        out = engine.step(slots, [r[(cut if b == 0 else 0):n] for b, (r, n) in enumerate(zip(reqs, lens))],
+                          [[n - 1 - (cut if b == 0 else 0)] for b, n in enumerate(lens)])
+        for b in range(len(reqs)):
+            rows[b].add(out[b], want[b][lens[b] - 1], "prompt")
+        for step in range(max(n_decode)):
+            live = [b for b in range(len(reqs)) if step < n_decode[b]]
+            out = engine.step([slots[b] for b in live], [[reqs[b][lens[b] + step]] for b in live])
+            for i, b in enumerate(live):
+                rows[b].add(out[i], want[b][lens[b] + step], f"decoded token {step}")
+            for b in live:
+                if step + 1 == n_decode[b]:
+                    engine.free_slot(slots[b])
+        for b in range(len(reqs)):
+            if n_decode[b] == 0:
+                engine.free_slot(slots[b])
+            rows[b].done()
+    engine.cache.check()
+    model.rt.check_status()

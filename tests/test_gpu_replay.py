@@ -85,7 +85,8 @@ def test_replay(tmp_path, dtype, name):
 
 def test_replay_reports_a_full_cache(tmp_path):
     folder = make_folder(tmp_path / "m", "A", seed=1)
-    step = {"step": 0, "entries": [{"id": "x", "tokens": [1] * 65, "want": []}], "end": []}
+    # the cache has pages for --max-tokens and one more for each of up to 64 live requests: 70 requests of a page each
+    step = {"step": 0, "entries": [{"id": f"x{i}", "tokens": [1] * 64, "want": []} for i in range(70)], "end": []}
     p = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", "float32",
                         "--out", str(tmp_path / "o"), "--max-tokens", "64"], input=json.dumps(step) + "\n",
                        capture_output=True, text=True, timeout=600)
