@@ -381,14 +381,16 @@ constexpr int kMaxTaps = 32;
 
 // One warp per (token, item): G query heads, G key heads, H value heads, and one item for the token's H decays and
 // write strengths.  xc [n_tok, C] receives the convolved, activated (and for q, k: normalised) channels, gb [n_tok,
-// 2 H] the decays g and then the strengths beta.  A token of no sequence (tok_seq < 0) gets zeros.
+// 2 H] the decays g and then the strengths beta.  A token of no sequence (tok_seq < 0) gets zeros.  With shift_here
+// (every sequence of the step brings ONE token, so a channel's kept inputs are read by one lane of one warp alone) that
+// lane also advances the channel's kept inputs by the token, which saves the launch of the kernel below.
 __global__ void __launch_bounds__(256)
 delta_prepare_kernel(const float* __restrict__ proj, int ld, const void* __restrict__ conv_w, int w_dt,
-                     const float* __restrict__ conv_state, long slot_stride, const int* __restrict__ tok_seq,
+                     float* conv_state, long slot_stride, const int* __restrict__ tok_seq,
                      const int* __restrict__ seq_slots, const int* __restrict__ cu_seqlens,
                      const void* __restrict__ a_log, const void* __restrict__ dt_bias, int p_dt,
                      float* __restrict__ xc, float* __restrict__ gb, long n_items, int H, int G, int d, int e, int taps,
-                     float q_scale) {
+                     float q_scale, int shift_here) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long item = (long)blockIdx.x * 8 + warp;
     if (item >= n_items) return;
@@ -419,7 +421,7 @@ delta_prepare_kernel(const float* __restrict__ proj, int ld, const void* __restr
         return;
     }
     const int local = t - cu_seqlens[seq];          // the token's place among its sequence's tokens of this step
-    const float* st = conv_state + (size_t)slot * slot_stride;
+    float* st = conv_state + (size_t)slot * slot_stride;
     float ss = 0.0f;
     for (int i = lane; i < len; i += 32) {
         const int ch = ch0 + i;
@@ -432,6 +434,10 @@ delta_prepare_kernel(const float* __restrict__ proj, int ld, const void* __restr
         const float y = acc / (1.0f + expf(0.0f - acc));
         dst[i] = y;
         ss = fmaf(y, y, ss);
+        if (shift_here && taps > 1) {       // local is 0: the kept inputs move up by one, the token's input comes last
+            for (int s = 0; s + 2 < taps; ++s) st[(size_t)s * C + ch] = st[(size_t)(s + 1) * C + ch];
+            st[(size_t)(taps - 2) * C + ch] = proj[(size_t)t * ld + ch];
+        }
     }
     if (is_v) return;
     ss = warp_sum(ss);
@@ -462,7 +468,7 @@ delta_conv_state_kernel(const float* __restrict__ proj, int ld, float* __restric
 extern "C" int nncpu_delta_prepare(const float* proj, int ld, const void* conv_w, int w_dt, float* conv_state,
                                    long slot_stride, const int* tok_seq, const int* seq_slots, const int* cu_seqlens, const void* a_log,
                                    const void* dt_bias, int p_dt, float* xc, float* gb, int n_tok, int n_seqs, int H,
-                                   int G, int d, int e, int taps, float q_scale, void* stream) {
+                                   int G, int d, int e, int taps, float q_scale, int one_token_each, void* stream) {
     NN_CHECK(n_tok >= 0 && n_seqs >= 0 && H > 0 && G > 0 && H % G == 0 && d > 0 && e > 0,
              "delta prepare: %d heads over %d query/key heads of %d x %d", H, G, d, e);
     NN_CHECK(taps >= 1 && taps <= kMaxTaps, "delta prepare: %d taps (1 to %d)", taps, kMaxTaps);
@@ -472,9 +478,9 @@ extern "C" int nncpu_delta_prepare(const float* proj, int ld, const void* conv_w
     const long n_items = (long)n_tok * (2 * G + H + 1);
     delta_prepare_kernel<<<(unsigned)((n_items + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
         proj, ld, conv_w, w_dt, conv_state, slot_stride, tok_seq, seq_slots, cu_seqlens, a_log, dt_bias, p_dt, xc, gb, n_items, H, G, d,
-        e, taps, q_scale);
+        e, taps, q_scale, one_token_each);
     NN_LAUNCH_OK("delta prepare");
-    if (taps > 1 && n_seqs > 0) {
+    if (taps > 1 && n_seqs > 0 && !one_token_each) {
         const long total = (long)n_seqs * C;
         delta_conv_state_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
             proj, ld, conv_state, slot_stride, seq_slots, cu_seqlens, n_seqs, C, taps);

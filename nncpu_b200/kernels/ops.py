@@ -817,13 +817,15 @@ def gla_output(o, proj, weight, eps: float, out, n_heads: int, d: int, e: int, g
 
 
 def delta_prepare(proj, conv_w, state, conv_col: int, tok_seq, seq_slots, cu_seqlens, a_log, dt_bias, xc, gb, n_seqs: int,
-                  n_heads: int, n_kv: int, d: int, e: int, taps: int) -> None:
+                  n_heads: int, n_kv: int, d: int, e: int, taps: int, one_token_each: bool = False) -> None:
     """What the gated delta rule's recurrence reads, from the projections: ``proj`` float32 [n, >= C + H e + 2 H] holds
     per token q (G d), k (G d), v (H e) (the C channels of the short convolutions), the output gate's logits (H e), the
     logits of beta (H) and the decays' inputs (H).  ``xc`` float32 [n, C] receives silu(conv(.)) with q and k made unit
     vectors per head (q also times d^-1/2), ``gb`` float32 [n, 2 H] the decays exp(-exp(A_log) softplus(a + dt_bias))
     and then beta = sigmoid(b).  ``conv_w`` [C, taps]; ``state`` float32 [slots, L] holds from lane ``conv_col`` of a
-    slot's row [taps - 1, C]: the sequence's last inputs; it is left advanced by the step's tokens."""
+    slot's row [taps - 1, C]: the sequence's last inputs; it is left advanced by the step's tokens.
+    ``one_token_each``: every sequence of the step brings exactly one token (the kept inputs then advance inside the one
+    kernel; otherwise a second kernel advances them after all tokens have read them)."""
     n = xc.shape[0]
     C = 2 * n_kv * d + n_heads * e
     assert proj.dtype == xc.dtype == gb.dtype == state.dtype == torch.float32 and proj.is_contiguous()
@@ -835,7 +837,8 @@ def delta_prepare(proj, conv_w, state, conv_col: int, tok_seq, seq_slots, cu_seq
     _call("recurrent", "nncpu_delta_prepare", _ptr(proj), _i(proj.shape[1]), _ptr(conv_w), _i(_code(conv_w)),
           None if (state.is_meta and _dry) else _vp(state.data_ptr() + 4 * conv_col), _l(state.shape[1]), _ptr(tok_seq), _ptr(seq_slots), _ptr(cu_seqlens), _ptr(a_log),
           _ptr(dt_bias), _i(_code(a_log)),
-          _ptr(xc), _ptr(gb), _i(n), _i(n_seqs), _i(n_heads), _i(n_kv), _i(d), _i(e), _i(taps), _f(d ** -0.5), _stream())
+          _ptr(xc), _ptr(gb), _i(n), _i(n_seqs), _i(n_heads), _i(n_kv), _i(d), _i(e), _i(taps), _f(d ** -0.5),
+          _i(one_token_each), _stream())
 
 
 def delta_scan(xc, gb, state, seq_slots, cu_seqlens, o, n_seqs: int, n_heads: int, n_kv: int, d: int, e: int) -> None:

@@ -98,7 +98,8 @@ class GatedDelta(Mixer):
         o = rt.empty(n, self.v_size, dtype=torch.float32)
         with rt.phase("delta_conv", nbytes=4.0 * (proj.numel() + xc.numel())):
             ops.delta_prepare(proj, self.w_conv, cache.state, self.state_floats, ctx.tok_seq, ctx.seq_slots, ctx.cu_seqlens,
-                              self.a_log, self.dt_bias, xc, gb, ctx.n_seqs, H, G, d, e, s.conv)
+                              self.a_log, self.dt_bias, xc, gb, ctx.n_seqs, H, G, d, e, s.conv,
+                              one_token_each=ctx.is_decode)
         with rt.phase("delta_scan", nbytes=state_bytes + 4.0 * (xc.numel() + o.numel()), flops=6.0 * n * H * d * e):
             ops.delta_scan(xc, gb, cache.state, ctx.seq_slots, ctx.cu_seqlens, o, ctx.n_seqs, H, G, d, e)
         with rt.phase("delta_gate"):

@@ -449,7 +449,8 @@ def test_delta_rule_remembers_a_write_far_back_and_padding_leaves_the_state_alon
         cu = i32([0, hi - lo] + [hi - lo + i + 1 for i in range(len(slots) - 1)])
         ts = i32([0] * (hi - lo) + list(range(1, len(slots))))
         xc, gb, out = torch.empty(n, C, device=DEV), torch.empty(n, 2 * H, device=DEV), torch.empty(n, H * e, device=DEV)
-        ops.delta_prepare(pj, conv_w.to(DEV), state, S, ts, i32(slots), cu, a_log.to(DEV), dt_bias.to(DEV), xc, gb, len(slots), H, G, d, e, taps)
+        ops.delta_prepare(pj, conv_w.to(DEV), state, S, ts, i32(slots), cu, a_log.to(DEV), dt_bias.to(DEV), xc, gb, len(slots), H, G, d, e, taps,
+                          one_token_each=hi - lo == 1)      # a decode step advances the kept inputs inside the one kernel
         ops.delta_scan(xc, gb, state, i32(slots), cu, out, len(slots), H, G, d, e)
         o[lo:hi] = out[:hi - lo]
         return out[hi - lo:]
