@@ -507,39 +507,43 @@ __device__ __forceinline__ void cp_async_wait_one_() { asm volatile("cp.async.wa
 // g and beta of a group of tokens are staged in shared memory by asynchronous copies, the next group's in flight under
 // this group's arithmetic.  The order of operations of a (sequence, head, column) does not depend on how the sequence
 // was cut into steps or on what else the step holds.  A negative slot (padding): zeros out, no state touched.
-template <int DR, int R>
+template <int DR, int R, int CPL>
 __global__ void __launch_bounds__(128)
 delta_scan_kernel(const float* __restrict__ xc, const float* __restrict__ gb, float* __restrict__ state,
                   long slot_stride, const int* __restrict__ seq_slots, const int* __restrict__ cu_seqlens, float* __restrict__ o, int H,
                   int G, int d, int e) {
     static_assert(DR % 4 == 0, "a lane keeps whole groups of four rows");
     constexpr int DP = DR * R;                      // rows the lanes cover (>= d; the rest hold zeros)
-    constexpr int CW = 32 / R;                      // columns a warp
+    constexpr int CW = CPL * 32 / R;                // columns a warp: CPL neighbouring ones a lane
     constexpr int COLS = 4 * CW;                    // columns a block
     constexpr int TB = DP <= 256 ? 8 : (DP <= 512 ? 4 : 2);       // tokens a group
     constexpr int BUF = TB * (2 * DP + COLS + 2);   // floats a buffer: k, q [TB][DP], v [TB][COLS], (g, beta) [TB]
     extern __shared__ __align__(16) float dsm_[];
     const int seq = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31, r = lane % R;
-    auto row_of = [&](int ii) { return ((ii >> 2) * R + r) * 4 + (ii & 3); };      // the row that S[ii] holds
-    const int col_local = warp * CW + lane / R, col0 = blockIdx.z * COLS, col = col0 + col_local;
+    auto row_of = [&](int ii) { return ((ii >> 2) * R + r) * 4 + (ii & 3); };      // the row that S[.][ii] holds
+    const int col_local = warp * CW + (lane / R) * CPL, col0 = blockIdx.z * COLS, col = col0 + col_local;
     const int t0 = cu_seqlens[seq], t1 = cu_seqlens[seq + 1];
     const int slot = seq_slots[seq];
     const int C = 2 * G * d + H * e;
     const bool wide = (d & 3) == 0 && (C & 3) == 0 && (reinterpret_cast<uintptr_t>(xc) & 15) == 0;
     if (slot < 0) {
-        if (r == 0 && col < e)
-            for (int t = t0; t < t1; ++t) o[(size_t)t * H * e + (size_t)h * e + col] = 0.0f;
+        if (r == 0)
+            for (int t = t0; t < t1; ++t)
+#pragma unroll
+                for (int cc = 0; cc < CPL; ++cc)
+                    if (col + cc < e) o[(size_t)t * H * e + (size_t)h * e + col + cc] = 0.0f;
         return;
     }
     const int kvh = h / (H / G);
     const size_t q_at = (size_t)kvh * d, k_at = (size_t)G * d + (size_t)kvh * d, v_at = 2 * (size_t)G * d + (size_t)h * e;
     float* s_head = state + (size_t)slot * slot_stride + (size_t)h * d * e;
-    float S[DR];
+    float S[CPL][DR];
 #pragma unroll
     for (int ii = 0; ii < DR; ++ii) {
         const int i = row_of(ii);
-        S[ii] = (i < d && col < e) ? s_head[(size_t)i * e + col] : 0.0f;
+#pragma unroll
+        for (int cc = 0; cc < CPL; ++cc) S[cc][ii] = (i < d && col + cc < e) ? s_head[(size_t)i * e + col + cc] : 0.0f;
     }
     for (int i = tid; i < 2 * BUF; i += 128) dsm_[i] = 0.0f;      // rows beyond d and columns beyond e stay zero
     __syncthreads();
@@ -588,56 +592,84 @@ delta_scan_kernel(const float* __restrict__ xc, const float* __restrict__ gb, fl
         const float* vb = qb + TB * DP;
         const float* gbb = vb + TB * COLS;
         // One token: the chain from token to token is S^T k (DR multiply-adds in four sums, log2(R) shuffles), u, and
-        // the update of S.  The lane's part of o = S^T q is returned; its sum over the lanes is off the chain.
-        auto token = [&](int tt) -> float {
-            const float g = gbb[tt * 2], beta = gbb[tt * 2 + 1], v = vb[tt * COLS + col_local];
+        // the update of S, once per column of the lane: the lane's columns are independent chains that share the
+        // loads of k and q and fill one another's waits.  The lane's parts of o = S^T q are left in os; their sums
+        // over the lanes are off the chain.
+        auto token = [&](int tt, float (&os)[CPL]) {
+            const float g = gbb[tt * 2], beta = gbb[tt * 2 + 1];
             float kk[DR];
-            float p[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            float p[CPL][4];
+#pragma unroll
+            for (int cc = 0; cc < CPL; ++cc) p[cc][0] = p[cc][1] = p[cc][2] = p[cc][3] = 0.0f;
 #pragma unroll
             for (int c = 0; c < DR / 4; ++c) {
                 const float4 k4 = *reinterpret_cast<const float4*>(kb + tt * DP + (c * R + r) * 4);
                 kk[4 * c] = k4.x; kk[4 * c + 1] = k4.y; kk[4 * c + 2] = k4.z; kk[4 * c + 3] = k4.w;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) p[j] = fmaf(kk[4 * c + j], S[4 * c + j], p[j]);
-            }
-            float ks = (p[0] + p[1]) + (p[2] + p[3]);
+                for (int cc = 0; cc < CPL; ++cc)
 #pragma unroll
-            for (int m = 1; m < R; m <<= 1) ks += __shfl_xor_sync(0xffffffffu, ks, m);
-            const float u = beta * (v - g * ks);       // S^T k of the decayed state is g times that of the old one
-            float a[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                    for (int j = 0; j < 4; ++j) p[cc][j] = fmaf(kk[4 * c + j], S[cc][4 * c + j], p[cc][j]);
+            }
+            float ks[CPL], u[CPL];
+#pragma unroll
+            for (int cc = 0; cc < CPL; ++cc) ks[cc] = (p[cc][0] + p[cc][1]) + (p[cc][2] + p[cc][3]);
+#pragma unroll
+            for (int m = 1; m < R; m <<= 1)
+#pragma unroll
+                for (int cc = 0; cc < CPL; ++cc) ks[cc] += __shfl_xor_sync(0xffffffffu, ks[cc], m);
+            // S^T k of the decayed state is g times that of the old one
+#pragma unroll
+            for (int cc = 0; cc < CPL; ++cc) u[cc] = beta * (vb[tt * COLS + col_local + cc] - g * ks[cc]);
+            float a[CPL][4];
+#pragma unroll
+            for (int cc = 0; cc < CPL; ++cc) a[cc][0] = a[cc][1] = a[cc][2] = a[cc][3] = 0.0f;
 #pragma unroll
             for (int c = 0; c < DR / 4; ++c) {
                 const float4 q4 = *reinterpret_cast<const float4*>(qb + tt * DP + (c * R + r) * 4);
                 const float qq[4] = {q4.x, q4.y, q4.z, q4.w};
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    S[4 * c + j] = fmaf(g, S[4 * c + j], kk[4 * c + j] * u);
-                    a[j] = fmaf(qq[j], S[4 * c + j], a[j]);
-                }
+                for (int cc = 0; cc < CPL; ++cc)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        S[cc][4 * c + j] = fmaf(g, S[cc][4 * c + j], kk[4 * c + j] * u[cc]);
+                        a[cc][j] = fmaf(qq[j], S[cc][4 * c + j], a[cc][j]);
+                    }
             }
-            return (a[0] + a[1]) + (a[2] + a[3]);
+#pragma unroll
+            for (int cc = 0; cc < CPL; ++cc) os[cc] = (a[cc][0] + a[cc][1]) + (a[cc][2] + a[cc][3]);
         };
         if (nt == TB) {
             // a whole group, unrolled: the next token's loads issue under this token's chain, and the sums for o of
             // all its tokens are added over the lanes together, as independent chains (the same additions in the same
             // order as one by one)
-            float os[TB];
+            float os[TB][CPL];
 #pragma unroll
-            for (int tt = 0; tt < TB; ++tt) os[tt] = token(tt);
+            for (int tt = 0; tt < TB; ++tt) token(tt, os[tt]);
 #pragma unroll
             for (int m = 1; m < R; m <<= 1)
 #pragma unroll
-                for (int tt = 0; tt < TB; ++tt) os[tt] += __shfl_xor_sync(0xffffffffu, os[tt], m);
-            if (r == 0 && col < e) {
+                for (int tt = 0; tt < TB; ++tt)
 #pragma unroll
-                for (int tt = 0; tt < TB; ++tt) o[(size_t)(g0 + tt) * H * e + (size_t)h * e + col] = os[tt];
+                    for (int cc = 0; cc < CPL; ++cc) os[tt][cc] += __shfl_xor_sync(0xffffffffu, os[tt][cc], m);
+            if (r == 0) {
+#pragma unroll
+                for (int tt = 0; tt < TB; ++tt)
+#pragma unroll
+                    for (int cc = 0; cc < CPL; ++cc)
+                        if (col + cc < e) o[(size_t)(g0 + tt) * H * e + (size_t)h * e + col + cc] = os[tt][cc];
             }
         } else {
             for (int tt = 0; tt < nt; ++tt) {
-                float os = token(tt);
+                float os[CPL];
+                token(tt, os);
 #pragma unroll
-                for (int m = 1; m < R; m <<= 1) os += __shfl_xor_sync(0xffffffffu, os, m);
-                if (r == 0 && col < e) o[(size_t)(g0 + tt) * H * e + (size_t)h * e + col] = os;
+                for (int m = 1; m < R; m <<= 1)
+#pragma unroll
+                    for (int cc = 0; cc < CPL; ++cc) os[cc] += __shfl_xor_sync(0xffffffffu, os[cc], m);
+                if (r == 0)
+#pragma unroll
+                    for (int cc = 0; cc < CPL; ++cc)
+                        if (col + cc < e) o[(size_t)(g0 + tt) * H * e + (size_t)h * e + col + cc] = os[cc];
             }
         }
         __syncthreads();             // the buffer is free for the group after next
@@ -645,25 +677,29 @@ delta_scan_kernel(const float* __restrict__ xc, const float* __restrict__ gb, fl
 #pragma unroll
     for (int ii = 0; ii < DR; ++ii) {
         const int i = row_of(ii);
-        if (i < d && col < e) s_head[(size_t)i * e + col] = S[ii];
+#pragma unroll
+        for (int cc = 0; cc < CPL; ++cc)
+            if (i < d && col + cc < e) s_head[(size_t)i * e + col + cc] = S[cc][ii];
     }
 }
 
-template <int DR, int R>
+template <int DR, int R, int CPL>
 static int launch_delta_scan(const float* xc, const float* gb, float* state, long slot_stride, const int* seq_slots, const int* cu_seqlens,
                              float* o, int n_seqs, int H, int G, int d, int e, cudaStream_t st) {
-    constexpr int DP = DR * R, COLS = 4 * (32 / R), TB = DP <= 256 ? 8 : (DP <= 512 ? 4 : 2);
+    constexpr int DP = DR * R, COLS = 4 * (CPL * 32 / R), TB = DP <= 256 ? 8 : (DP <= 512 ? 4 : 2);
     constexpr size_t smem = (size_t)2 * TB * (2 * DP + COLS + 2) * sizeof(float);
     static_assert(smem <= 48 * 1024, "the staging buffers fit the default shared memory");
     dim3 grid(n_seqs, H, (e + COLS - 1) / COLS);
-    delta_scan_kernel<DR, R><<<grid, 128, smem, st>>>(xc, gb, state, slot_stride, seq_slots, cu_seqlens, o, H, G, d, e);
+    delta_scan_kernel<DR, R, CPL><<<grid, 128, smem, st>>>(xc, gb, state, slot_stride, seq_slots, cu_seqlens, o, H, G, d, e);
     return 0;
 }
 
 // Blocks of one sequence that the choice of lanes a column aims for: two thirds of the SMs of a 148-SM part.
 constexpr long kDeltaBlocksWanted = 96;
 static int g_delta_lanes = 0;    // a measurement's override of the lanes a column (0: the rule below)
+static int g_delta_cpl = 0;      // and of the columns a lane (0: the rule below)
 extern "C" void nncpu_delta_scan_force_lanes(int lanes) { g_delta_lanes = lanes; }
+extern "C" void nncpu_delta_scan_force_columns(int cpl) { g_delta_cpl = cpl; }
 
 extern "C" int nncpu_delta_scan(const float* xc, const float* gb, float* state, long slot_stride, const int* seq_slots,
                                 const int* cu_seqlens, float* o, int n_seqs, int H, int G, int d, int e, void* stream) {
@@ -685,9 +721,18 @@ extern "C" int nncpu_delta_scan(const float* xc, const float* gb, float* state, 
         R = g_delta_lanes;
     else
         while (R < 32 && R * 2 <= DP / 4 && (long)H * ((e + 128 / R - 1) / (128 / R)) < kDeltaBlocksWanted) R *= 2;
+    // Two columns a lane with twice the lanes a column: the same blocks, warps and registers, but a warp then walks
+    // two independent chains that share their loads of k and q.  It pays where the blocks suffice without more lanes
+    // (32 heads of 128 x 128: 8 sequences of 512 tokens 847 -> 556 us, one of 2 048 tokens 591 -> 551 us), not where
+    // the lanes were raised to get blocks (16 heads, lanes raised to 8: 455 us with one column a lane, 513 with two).
+    int CPL = (R == (DP / 32 < 4 ? 4 : DP / 32) && 2 * R <= 32 && 2 * R <= DP / 4) ? 2 : 1;
+    if (g_delta_cpl == 1 || g_delta_cpl == 2) CPL = (g_delta_cpl == 2 && 2 * R <= 32 && 2 * R <= DP / 4) ? 2 : 1;
+    if (CPL == 2) R *= 2;
 #define NN_DELTA(DP_, R_)                                                                                              \
-    if (DP == DP_ && R == R_)                                                                                          \
-        launch_delta_scan<DP_ / R_, R_>(xc, gb, state, slot_stride, seq_slots, cu_seqlens, o, n_seqs, H, G, d, e, st);
+    if (DP == DP_ && R == R_ && CPL == 1)                                                                              \
+        launch_delta_scan<DP_ / R_, R_, 1>(xc, gb, state, slot_stride, seq_slots, cu_seqlens, o, n_seqs, H, G, d, e, st); \
+    if (DP == DP_ && R == R_ && CPL == 2)                                                                              \
+        launch_delta_scan<DP_ / R_, R_, 2>(xc, gb, state, slot_stride, seq_slots, cu_seqlens, o, n_seqs, H, G, d, e, st);
     NN_DELTA(32, 4) NN_DELTA(32, 8)
     NN_DELTA(64, 4) NN_DELTA(64, 8) NN_DELTA(64, 16)
     NN_DELTA(128, 4) NN_DELTA(128, 8) NN_DELTA(128, 16) NN_DELTA(128, 32)
