@@ -381,16 +381,17 @@ constexpr int kMaxTaps = 32;
 
 // One warp per (token, item): G query heads, G key heads, H value heads, and one item for the token's H decays and
 // write strengths.  xc [n_tok, C] receives the convolved, activated (and for q, k: normalised) channels, gb [n_tok,
-// 2 H] the decays g and then the strengths beta.  A token of no sequence (tok_seq < 0) gets zeros.  With shift_here
+// 2 H] the decays g and then the strengths beta.  A token of no sequence (tok_seq < 0) gets zeros.  With kShiftHere
 // (every sequence of the step brings ONE token, so a channel's kept inputs are read by one lane of one warp alone) that
 // lane also advances the channel's kept inputs by the token, which saves the launch of the kernel below.
+template <bool kShiftHere>
 __global__ void __launch_bounds__(256)
 delta_prepare_kernel(const float* __restrict__ proj, int ld, const void* __restrict__ conv_w, int w_dt,
                      float* conv_state, long slot_stride, const int* __restrict__ tok_seq,
                      const int* __restrict__ seq_slots, const int* __restrict__ cu_seqlens,
                      const void* __restrict__ a_log, const void* __restrict__ dt_bias, int p_dt,
                      float* __restrict__ xc, float* __restrict__ gb, long n_items, int H, int G, int d, int e, int taps,
-                     float q_scale, int shift_here) {
+                     float q_scale) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long item = (long)blockIdx.x * 8 + warp;
     if (item >= n_items) return;
@@ -422,19 +423,21 @@ delta_prepare_kernel(const float* __restrict__ proj, int ld, const void* __restr
     }
     const int local = t - cu_seqlens[seq];          // the token's place among its sequence's tokens of this step
     float* st = conv_state + (size_t)slot * slot_stride;
+    const float* __restrict__ st_kept = st;     // what the kernel that does not advance the kept inputs reads them through
     float ss = 0.0f;
     for (int i = lane; i < len; i += 32) {
         const int ch = ch0 + i;
         float acc = 0.0f;
         for (int j = 0; j < taps; ++j) {
             const int at = local - (taps - 1) + j;
-            const float x = at >= 0 ? proj[(size_t)(t - local + at) * ld + ch] : st[(size_t)(taps - 1 + at) * C + ch];
+            const float x = at >= 0 ? proj[(size_t)(t - local + at) * ld + ch]
+                                    : (kShiftHere ? st : st_kept)[(size_t)(taps - 1 + at) * C + ch];
             acc = fmaf(ld_f(conv_w, (size_t)ch * taps + j, w_dt), x, acc);
         }
         const float y = acc / (1.0f + expf(0.0f - acc));
         dst[i] = y;
         ss = fmaf(y, y, ss);
-        if (shift_here && taps > 1) {       // local is 0: the kept inputs move up by one, the token's input comes last
+        if (kShiftHere && taps > 1) {       // local is 0: the kept inputs move up by one, the token's input comes last
             for (int s = 0; s + 2 < taps; ++s) st[(size_t)s * C + ch] = st[(size_t)(s + 1) * C + ch];
             st[(size_t)(taps - 2) * C + ch] = proj[(size_t)t * ld + ch];
         }
@@ -476,9 +479,14 @@ extern "C" int nncpu_delta_prepare(const float* proj, int ld, const void* conv_w
     NN_CHECK(ld >= C + H * e + 2 * H, "delta prepare: rows of %d floats", ld);
     if (n_tok == 0) return 0;
     const long n_items = (long)n_tok * (2 * G + H + 1);
-    delta_prepare_kernel<<<(unsigned)((n_items + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
-        proj, ld, conv_w, w_dt, conv_state, slot_stride, tok_seq, seq_slots, cu_seqlens, a_log, dt_bias, p_dt, xc, gb, n_items, H, G, d,
-        e, taps, q_scale, one_token_each);
+    if (one_token_each)
+        delta_prepare_kernel<true><<<(unsigned)((n_items + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
+            proj, ld, conv_w, w_dt, conv_state, slot_stride, tok_seq, seq_slots, cu_seqlens, a_log, dt_bias, p_dt, xc, gb, n_items, H,
+            G, d, e, taps, q_scale);
+    else
+        delta_prepare_kernel<false><<<(unsigned)((n_items + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
+            proj, ld, conv_w, w_dt, conv_state, slot_stride, tok_seq, seq_slots, cu_seqlens, a_log, dt_bias, p_dt, xc, gb, n_items, H,
+            G, d, e, taps, q_scale);
     NN_LAUNCH_OK("delta prepare");
     if (taps > 1 && n_seqs > 0 && !one_token_each) {
         const long total = (long)n_seqs * C;
