@@ -8,6 +8,8 @@ GFLOP/s for its row kernels and one attention block.
     python -m nncpu_b200.kernels.microbench attention-decode BATCH CONTEXT [--splits S] [--cluster] [--from-projections]
     python -m nncpu_b200.kernels.microbench attention-prefill BATCH TOKENS
     python -m nncpu_b200.kernels.microbench rmsnorm ROWS DIM
+    python -m nncpu_b200.kernels.microbench gla BATCH TOKENS [--columns 2|4]
+    python -m nncpu_b200.kernels.microbench delta BATCH TOKENS [--lanes 4|8|16|32] [--columns 1|2]
 
 Timing: the kernel is captured in a CUDA graph over enough different buffers
 that no launch finds its operands in L2, replayed, and timed with CUDA events.
@@ -220,6 +222,25 @@ def gla(args) -> None:
           f"{nbytes / ms / 1e6:.0f} GB/s of inputs and outputs")
 
 
+def delta(args) -> None:
+    """The gated delta rule's recurrence over `tokens` tokens of `batch` sequences (the scan kernel; a decode step
+    is the same kernel with one token a sequence)."""
+    b, t, h, g, d, e = args.batch, args.tokens, args.heads, args.kv_heads, args.key_dim, args.value_dim
+    n, c = b * t, 2 * g * d + h * e
+    ops.delta_scan_force(args.lanes, args.columns)
+    xc = torch.randn(n, c, device=DEV) * 0.1
+    gb = torch.rand(n, 2 * h, device=DEV)
+    state = torch.zeros(b + 1, h * d * e, device=DEV)
+    slots = torch.arange(b, dtype=torch.int32, device=DEV)
+    cu = torch.arange(0, n + 1, t, dtype=torch.int32, device=DEV)
+    o = torch.empty(n, h * e, device=DEV)
+    ms = _time([lambda: ops.delta_scan(xc, gb, state, slots, cu, o, b, h, g, d, e)], args.once)
+    ops.delta_scan_force()
+    nbytes = 4.0 * (n * (2 * d * g + e * h) + gb.numel() + o.numel()) + 8.0 * b * h * d * e
+    print(f"delta scan batch={b} tokens={t} heads={h} on {g} d={d} e={e}: {ms * 1e3:.1f} us, "
+          f"{3.0 * n * h * d * e / ms / 1e9:.2f} T multiply-adds/s, {nbytes / ms / 1e6:.0f} GB/s of inputs, outputs and state")
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--once", action="store_true", help="three plain launches, no timing (for a profiler)")
@@ -262,6 +283,13 @@ def main(argv=None) -> int:
     p.add_argument("--value-dim", type=int, default=256)
     p.add_argument("--columns", type=int, default=0, choices=[0, 2, 4], help="columns of the state a lane (0: by the grid's size)")
     p.set_defaults(fn=gla)
+    p = sub.add_parser("delta")
+    p.add_argument("batch", type=int); p.add_argument("tokens", type=int)
+    p.add_argument("--heads", type=int, default=16); p.add_argument("--kv-heads", type=int, default=8)
+    p.add_argument("--key-dim", type=int, default=128); p.add_argument("--value-dim", type=int, default=128)
+    p.add_argument("--lanes", type=int, default=0, choices=[0, 4, 8, 16, 32], help="lanes a column of the state (0: by the layer's sizes)")
+    p.add_argument("--columns", type=int, default=0, choices=[0, 1, 2], help="columns of the state a lane (0: by the layer's sizes)")
+    p.set_defaults(fn=delta)
     args = ap.parse_args(argv)
     if args.no_overlap:
         ops.launch_overlap(False)

@@ -841,6 +841,15 @@ def delta_prepare(proj, conv_w, state, conv_col: int, tok_seq, seq_slots, cu_seq
           _i(one_token_each), _stream())
 
 
+def delta_scan_force(lanes: int = 0, columns: int = 0) -> None:
+    """For measurements: the delta rule's scan runs with ``lanes`` lanes a column (a power of two from 4 to 32, before
+    the doubling that goes with two columns a lane) and 1 or 2 ``columns`` a lane, whatever the layer's sizes; 0: by the
+    launcher's rule."""
+    lib = library.load("recurrent")
+    lib.nncpu_delta_scan_force_lanes(ctypes.c_int(int(lanes)))
+    lib.nncpu_delta_scan_force_columns(ctypes.c_int(int(columns)))
+
+
 def delta_scan(xc, gb, state, seq_slots, cu_seqlens, o, n_seqs: int, n_heads: int, n_kv: int, d: int, e: int) -> None:
     """The gated delta rule over the step's tokens, sequence by sequence in order: per head S <- g S;
     u = beta (v - S^T k); S <- S + k u^T; o = S^T q, with q, k, v from ``xc`` and g, beta from ``gb`` as
