@@ -59,6 +59,10 @@ class Attention(Mixer):
         # keeps a prompt step off the fused q/k/v epilogue of the projection (which knows neither): the temperature is
         # applied where q is made (in a decode step: inside the attention kernel that starts from the projections),
         # the bias inside the attention kernels (tcgen05 for prompts, mma.sync for decode steps and short portions).
+        # Values that are the keys and an output gate keep a prompt step off that epilogue too (it appends a value of
+        # its own and knows no rows of gate logits); a decode step has them inside the attention kernel that starts
+        # from the projections.  A sink is a matter of the attention kernels alone, and all of them take it; the one
+        # design that has sinks has the other two as well, so a sink keeps to their path.
         self.plain_core = self.v_dim != s.head_dim
         self.unfused = (self.plain_core or s.slope_base != 0.0 or s.q_temp_coef != 0.0 or s.values_are_keys or s.sink
                         or s.out_gate)
