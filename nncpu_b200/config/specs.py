@@ -19,13 +19,16 @@ from typing import Optional, Tuple
 @dataclass(frozen=True)
 class NormSpec:
     """A normalisation over a vector of ``size`` lanes, weights at ``name + suffix``.  ``offset`` is added to
-    the stored weight before it multiplies (1.0 for weights that are stored around zero)."""
+    the stored weight before it multiplies (1.0 for weights that are stored around zero).  ``kind`` "rmsnorm":
+    x / sqrt(mean(x^2) + eps) * w.  ``kind`` "layernorm": (x - mean) / sqrt(var + eps) * w + b with var the mean of the
+    squared deviations and the bias b at ``name + suffix + bias_suffix``."""
     kind: str
     size: int
     eps: float
     name: str  # tensor name prefix, e.g. "model.layers.0.input_layernorm"
     suffix: str = ".weight"
     offset: float = 0.0
+    bias_suffix: str = ".b"
 
 
 @dataclass(frozen=True)
@@ -111,6 +114,35 @@ class LatentAttentionSpec(MixerSpec):
 
 
 @dataclass(frozen=True)
+class RetentionSpec(MixerSpec):
+    """Retention, a recurrent mixer: linear attention with one fixed decay per head and neither softmax nor
+    denominator.  q, k (``n_heads`` x ``key_dim``) and v (``n_heads`` x ``value_dim``) are projections without biases;
+    q and k are rotated by ``position`` (optional), k is then multiplied by key_dim^-1/2; per head
+    S_t = decays[h] S_(t-1) + k_t v_t^T, o_t = S_t^T q_t.  Every head's o is divided by its root mean square (``eps``,
+    no weight); the concatenated heads are multiplied by silu(W_g h) and projected back (``<name>.q / .k / .v / .g /
+    .o``).  The state is 32-bit."""
+    hidden_size: int = 0
+    n_heads: int = 0
+    key_dim: int = 0
+    value_dim: int = 0
+    decays: Tuple[float, ...] = ()
+    position: Optional[PositionSpec] = None
+    eps: float = 1e-6
+
+
+@dataclass(frozen=True)
+class MixerPairSpec(MixerSpec):
+    """Two mixers side by side that read the same input: the result is ``weight`` times the sum of their outputs, each
+    first RMS-normed over the model width (``eps``) with a plain weight of its own, ``<name>.<left|right>.out``; the
+    mixers' own tensors lie under ``<name>.left`` and ``<name>.right``."""
+    hidden_size: int = 0
+    left: Optional[MixerSpec] = None
+    right: Optional[MixerSpec] = None
+    eps: float = 1e-6
+    weight: float = 0.5
+
+
+@dataclass(frozen=True)
 class GatedDeltaSpec(MixerSpec):
     """The gated delta rule, a recurrent mixer: per head a state S of ``key_dim`` x ``value_dim`` 32-bit numbers.
     q and k have ``n_kv_heads`` heads (head h of ``n_heads`` uses q/k head h // (n_heads / n_kv_heads)), v has
@@ -118,7 +150,12 @@ class GatedDeltaSpec(MixerSpec):
     (x / sqrt(sum x^2 + 1e-6); q also times key_dim^-1/2).  Per token and head: beta = sigmoid(W_b h),
     g = exp(-exp(A_log) softplus(W_a h + dt_bias)); S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q.
     The heads' outputs are RMS-normed (``eps``, one weight of ``value_dim`` lanes), gated by silu(W_g h) and projected
-    back.  The last ``conv`` - 1 inputs of the convolutions are state too."""
+    back.  The last ``conv`` - 1 inputs of the convolutions are state too.
+
+    ``channel_decay``: one decay per head AND key channel, acting on the rows of S,
+    g = exp(-exp(A_log_h) softplus(W_a2 (W_a1 h) + dt_bias)) laid out heads x key_dim (``<name>.a1`` [r, hidden],
+    ``.a2`` [H key_dim, r], ``.dt_bias`` [H key_dim]; the rank r is what the file's tensors have), and the output gate is
+    sigmoid(W_g2 (W_g1 h)) laid out heads x value_dim (``.g1``, ``.g2``) in place of silu(W_g h)."""
     hidden_size: int = 0
     n_heads: int = 0
     n_kv_heads: int = 0
@@ -126,6 +163,9 @@ class GatedDeltaSpec(MixerSpec):
     value_dim: int = 0
     conv: int = 0
     eps: float = 1e-6
+    channel_decay: bool = False
+    decay_rank: int = 0     # 0: what the file's tensors have
+    gate_rank: int = 0
 
 
 @dataclass(frozen=True)
@@ -164,7 +204,13 @@ class GatedMlpSpec(FeedForwardSpec):
 class RoutedExpertsSpec(FeedForwardSpec):
     """``n_experts`` small gated feed-forwards (``<name>.e<i>.gate / .up / .down``) of which every token uses the
     ``top`` with the largest router logits (``<name>.router`` with the bias ``<name>.router.b``, in 32-bit), weighted
-    by the softmax over the chosen logits alone; plus an optional ``shared`` gated feed-forward that every token runs."""
+    by the softmax over the chosen logits alone; plus an optional ``shared`` gated feed-forward that every token runs.
+
+    ``scores`` "all": the scores are the softmax over ALL experts' logits; the ``top`` experts with the largest scores
+    are chosen, and their weights are their scores divided by the sum of the chosen scores (+ 1e-20), times
+    ``weight_scale``.  With ``n_groups`` > 1 the experts form that many equal groups of neighbours, a group's score is
+    its largest score, and only experts of the ``keep_groups`` best groups can be chosen.  ``router_bias`` False: the
+    router has no bias tensor.  ``out_scale`` multiplies what the part adds to the stream."""
     hidden_size: int = 0
     intermediate_size: int = 0
     n_experts: int = 0
@@ -172,15 +218,38 @@ class RoutedExpertsSpec(FeedForwardSpec):
     activation: str = "swish_clamp"
     limit: float = 0.0
     shared: Optional[GatedMlpSpec] = None
+    scores: str = "chosen"
+    n_groups: int = 1
+    keep_groups: int = 1
+    weight_scale: float = 1.0
+    router_bias: bool = True
+    out_scale: float = 1.0
 
 
 @dataclass(frozen=True)
 class DenseMlpSpec(FeedForwardSpec):
-    """down(act(up(x))) with biases on both products; ``activation`` "xielu" has two learned numbers at
-    ``<name>.act``."""
+    """down(act(up(x))) with biases on both products (``bias`` False: without); ``activation`` "xielu" has two learned
+    numbers at ``<name>.act``, "relu2" is the square of relu."""
     hidden_size: int = 0
     intermediate_size: int = 0
     activation: str = "xielu"
+    bias: bool = True
+
+
+@dataclass(frozen=True)
+class TokenSideSpec:
+    """A per-layer input from the token itself, added to the stream at the end of a layer: with e the lanes
+    [``col``, ``col`` + ``dim``) of row ``token`` of the table ``table`` [vocab, ``table_width``],
+    y = W_proj (gelu_tanh(W_gate x) * e) and x <- x + mult * y / sqrt(mean(y^2) + eps) * w
+    (``<name>.gate`` [dim, hidden], ``.proj`` [hidden, dim], ``.norm`` [hidden]; mult is the block's ``residual_mult``)."""
+    name: str
+    table: str
+    table_width: int
+    col: int
+    dim: int
+    hidden_size: int
+    vocab_size: int
+    eps: float = 1e-6
 
 
 @dataclass(frozen=True)
@@ -190,7 +259,9 @@ class BlockSpec:
     x += norm1_post(mixer(norm1(x))); x += norm2_post(feed_forward(norm2(x))), and a layer without a
     feed-forward (``feed_forward`` None) has the first sublayer only.  ``kind`` "parallel": both sublayers read the
     stream as it enters the layer, x += mixer(norm1(x)) + feed_forward(norm2(x)); without a feed-forward norm2 is not used (its tensor is optional);
-    a "parallel" layer with a feed-forward and ``norm2`` None has one norm, whose output both sublayers read."""
+    a "parallel" layer with a feed-forward and ``norm2`` None has one norm, whose output both sublayers read.
+    ``residual_mult`` m ("prenorm"): x += m * mixer(norm1(x)); x += m * feed_forward(norm2(x)), and a "prenorm" layer
+    may go without a feed-forward.  ``side`` ("prenorm"): a per-layer token input after the feed-forward."""
     kind: str
     norm1: NormSpec
     mixer: MixerSpec
@@ -198,16 +269,21 @@ class BlockSpec:
     feed_forward: Optional[FeedForwardSpec] = None
     norm1_post: Optional[NormSpec] = None
     norm2_post: Optional[NormSpec] = None
+    residual_mult: float = 1.0
+    side: Optional[TokenSideSpec] = None
 
 
 @dataclass(frozen=True)
 class StreamInjection:
     """What is added to the residual stream right before a schedule entry runs: with ``embedding`` the stream as the
-    embedding left it (before the first layer), and row ``row`` of the tensor ``table`` [``n_rows``, hidden]."""
+    embedding left it (before the first layer), and row ``row`` of the tensor ``table`` [``n_rows``, hidden].
+    ``mix`` (a tensor [hidden, 2 hidden]): first the stream becomes W_mix [x; x0], x0 the stream as the embedding left
+    it (x's columns first); the table's row is added after that."""
     embedding: bool = False
     table: Optional[str] = None
     n_rows: int = 0
     row: int = 0
+    mix: Optional[str] = None
 
 
 @dataclass(frozen=True)
@@ -231,6 +307,13 @@ class EmbeddingSpec:
     suffix: str = ".weight"
     positions: Optional[str] = None   # tensor name of a table of learned position vectors [n_positions, hidden],
     n_positions: int = 0              # added (unscaled) to the embedding rows; sequences cannot outgrow it
+    # A hashed embedding of the pair (previous token, token), added to the embedding row: row
+    # (previous * pair_mul_prev + token * pair_mul_cur) mod pair_buckets of the tensor ``pair_table``
+    # [pair_buckets + 1, hidden]; a sequence's first token takes the last row.  The previous token is per-sequence state.
+    pair_table: Optional[str] = None
+    pair_buckets: int = 0
+    pair_mul_prev: int = 0
+    pair_mul_cur: int = 0
 
 
 @dataclass(frozen=True)

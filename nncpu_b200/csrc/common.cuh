@@ -115,6 +115,7 @@ struct NormFusion {
 };
 
 constexpr int kActNone = 0, kActXielu = 1;
+constexpr int kActRelu2 = 4;      // the square of relu (plain epilogue, like xIELU; no numbers of its own)
 // with the gated epilogue (act(gate) * up; kActNone there is silu(g) u): the tanh form of GELU, and the clamped
 // g sigmoid(1.702 g) (u + 1) with its limit in act_a
 constexpr int kActGateGelu = 2, kActGateSwishClamp = 3;
@@ -122,6 +123,20 @@ constexpr int kActGateGelu = 2, kActGateSwishClamp = 3;
 // xIELU: a z^2 + z / 2 above zero, b (exp(z) - 1 - z) + z / 2 below, with a = softplus(p), b = 1/2 + softplus(q).
 __device__ __forceinline__ float xielu_f(float z, float a, float b) {
     return z > 0.0f ? fmaf(a * z, z, 0.5f * z) : fmaf(b, expm1f(z) - z, 0.5f * z);
+}
+
+// An activation of the plain epilogue by its code: xIELU, or the square of relu.
+__device__ __forceinline__ float plain_act_f(float z, int act, float a, float b) {
+    if (act == kActRelu2) {
+        const float r = fmaxf(z, 0.0f);
+        return r * r;
+    }
+    return act == kActXielu ? xielu_f(z, a, b) : z;
+}
+
+// The tanh form of GELU: z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * fmaf(0.044715f * z * z, z, z)));
 }
 
 // A non-negative float into its row's accumulator: value = mantissa * 2^(E - 150) with E = 32 * bin + shift.

@@ -140,9 +140,9 @@ __device__ __forceinline__ void store16(const GemmParams& p, int a_row, int b0, 
 #pragma unroll
                 for (int j = 0; j < 16; ++j) v[j] += ld_f(p.bias, b0 + j, p.bias_dt);
             }
-            if (p.nf.act == kActXielu) {
+            if (p.nf.act == kActXielu || p.nf.act == kActRelu2) {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) v[j] = xielu_f(v[j], p.nf.act_a, p.nf.act_b);
+                for (int j = 0; j < 16; ++j) v[j] = plain_act_f(v[j], p.nf.act, p.nf.act_a, p.nf.act_b);
             }
             if (p.out_dt == DT_F32) {
                 float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + o);
@@ -187,7 +187,7 @@ __device__ __forceinline__ void store16(const GemmParams& p, int a_row, int b0, 
             if (col >= p.rows_b) break;
             float x = v[j];
             if (p.bias) x += ld_f(p.bias, col, p.bias_dt);
-            if (p.nf.act == kActXielu) x = xielu_f(x, p.nf.act_a, p.nf.act_b);
+            if (p.nf.act == kActXielu || p.nf.act == kActRelu2) x = plain_act_f(x, p.nf.act, p.nf.act_a, p.nf.act_b);
             if (p.accumulate) x += ld_f(p.out, o + j, p.out_dt);
             st_f(p.out, o + j, p.out_dt, x);
         }
@@ -206,7 +206,7 @@ __device__ __forceinline__ void store16(const GemmParams& p, int a_row, int b0, 
             const int tok = b0 + j;
             if (tok >= p.rows_b || j >= ncols) break;
             float x = v[j] + b;
-            if (p.nf.act == kActXielu) x = xielu_f(x, p.nf.act_a, p.nf.act_b);
+            if (p.nf.act == kActXielu || p.nf.act == kActRelu2) x = plain_act_f(x, p.nf.act, p.nf.act_a, p.nf.act_b);
             st_f(p.out, (size_t)tok * p.ldc + a_row, p.out_dt, x + old[j]);
         }
     }
@@ -1119,7 +1119,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const int tok = n0 + c_begin + j;
                     const bool ok = j < n && tok < p.rows_b;        // the same for the whole warp
                     float x = v[j] + b;
-                    if (p.nf.act == kActXielu) x = xielu_f(x, p.nf.act_a, p.nf.act_b);
+                    if (p.nf.act == kActXielu || p.nf.act == kActRelu2) x = plain_act_f(x, p.nf.act, p.nf.act_a, p.nf.act_b);
                     const float y = x + old[j];
                     if (ok && a_ok) st_f(p.out, (size_t)tok * p.ldc + a_row, p.out_dt, y);
                     if (p.nf.xg_out != nullptr && ok) {
@@ -2015,7 +2015,7 @@ extern "C" int nncpu_linear_tc(const void* X, const void* W, const void* bias, i
         p.nf.bins_in = (const unsigned long long*)bins_in;
         p.nf.eps = eps;
     }
-    NN_CHECK(act == kActNone || (act == kActXielu && epilogue == kPlain && !accumulate && xg_out == nullptr) ||
+    NN_CHECK(act == kActNone || ((act == kActXielu || act == kActRelu2) && epilogue == kPlain && !accumulate && xg_out == nullptr) ||
                  ((act == kActGateGelu || act == kActGateSwishClamp) && epilogue == kSwiglu),
              "gemm: activation %d goes with the plain epilogue (without accumulation or a norm after it) or, as a gate, with the gated one", act);
     p.nf.act = act; p.nf.act_a = act_a; p.nf.act_b = act_b;

@@ -1926,26 +1926,108 @@ __device__ __forceinline__ void route_top(float* z, int n_experts, int top, int*
     for (int c = lane; c < top; c += 32) weights[c] *= inv;
 }
 
+// Scores over ALL experts: s = softmax(z).  The experts form n_groups equal groups of neighbours; a group's score is its
+// largest score, and only experts of the `keep` best groups can be chosen (n_groups <= 1: no groups).  The weights of the
+// chosen are their scores divided by the sum of the chosen scores (+ 1e-20), times `scale`.  One warp; z is overwritten;
+// gbuf holds n_groups floats.  The softmax does not change an order, so groups and experts are picked by their logits.
+__device__ __forceinline__ void route_top_all(float* z, float* gbuf, int n_experts, int top, int n_groups, int keep,
+                                              float scale, int* __restrict__ ids, float* __restrict__ weights, int lane) {
+    float zmax = -INFINITY;
+    for (int e = lane; e < n_experts; e += 32) zmax = fmaxf(zmax, z[e]);
+    zmax = warp_max(zmax);
+    float den = 0.0f;
+    for (int e = lane; e < n_experts; e += 32) den += expf(z[e] - zmax);
+    den = warp_sum(den);
+    if (n_groups > 1 && keep < n_groups) {
+        const int per = n_experts / n_groups;
+        for (int g = lane; g < n_groups; g += 32) {
+            float m = -INFINITY;
+            for (int j = 0; j < per; ++j) m = fmaxf(m, z[g * per + j]);
+            gbuf[g] = m;
+        }
+        __syncwarp();
+        for (int c = 0; c < keep; ++c) {
+            float best = -INFINITY;
+            int at = n_groups;
+            for (int g = lane; g < n_groups; g += 32) {
+                const float v = gbuf[g];
+                if (v > best || (v == best && g < at)) { best = v; at = g; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+                if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+            }
+            if (at < n_groups && lane == 0) gbuf[at] = __int_as_float(0x7FC00000);    // kept: NaN marks it
+            __syncwarp();
+        }
+        for (int e = lane; e < n_experts; e += 32)
+            if (gbuf[e / per] == gbuf[e / per]) z[e] = __int_as_float(0x7FC00000);      // not kept: cannot be chosen
+        __syncwarp();
+    }
+    float sum = 0.0f;
+    for (int c = 0; c < top; ++c) {
+        float best = -INFINITY;
+        int at = n_experts;
+        for (int e = lane; e < n_experts; e += 32) {
+            const float v = z[e];
+            if (v > best || (v == best && e < at)) { best = v; at = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+        }
+        if (at >= n_experts) at = 0;
+        const float w = expf(best - zmax) / den;
+        sum += w;
+        if (lane == 0) {
+            ids[c] = at;
+            weights[c] = w;
+            z[at] = __int_as_float(0x7FC00000);
+        }
+        __syncwarp();
+    }
+    const float inv = scale / (sum + 1e-20f);
+    for (int c = lane; c < top; c += 32) weights[c] *= inv;
+}
+
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const float* __restrict__ logits, int n_tok, int n_experts, int top, int* __restrict__ ids,
-                 float* __restrict__ weights) {
+                 float* __restrict__ weights, int all_scores, int n_groups, int keep, float scale) {
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * (blockDim.x >> 5) + warp;
     if (t >= n_tok) return;
-    float* z = smem + (size_t)warp * n_experts;
+    float* z = smem + (size_t)warp * (n_experts + n_groups);
     for (int e = lane; e < n_experts; e += 32) z[e] = logits[(size_t)t * n_experts + e];
     __syncwarp();
-    route_top(z, n_experts, top, ids + (size_t)t * top, weights + (size_t)t * top, lane);
+    if (all_scores)
+        route_top_all(z, z + n_experts, n_experts, top, n_groups, keep, scale, ids + (size_t)t * top,
+                      weights + (size_t)t * top, lane);
+    else
+        route_top(z, n_experts, top, ids + (size_t)t * top, weights + (size_t)t * top, lane);
+}
+
+// Whether a choice among groups can be made: equal groups, and the kept ones hold enough experts.
+static bool route_groups_ok(int n_experts, int top, int n_groups, int keep) {
+    if (n_groups <= 1) return true;
+    return n_experts % n_groups == 0 && keep >= 1 && keep <= n_groups && (long)keep * (n_experts / n_groups) >= top;
 }
 
 extern "C" int nncpu_moe_route(const float* logits, int n_tok, int n_experts, int top, int* ids, float* weights,
-                               void* stream) {
+                               int all_scores, int n_groups, int keep, float scale, void* stream) {
     NN_CHECK(n_tok >= 0 && n_experts > 0 && n_experts <= kRouteMaxExperts && top > 0 && top <= n_experts,
              "router: %d tokens, the top %d of %d experts (at most %d)", n_tok, top, n_experts, kRouteMaxExperts);
+    NN_CHECK(all_scores ? route_groups_ok(n_experts, top, n_groups, keep) : n_groups <= 1,
+             "router: the %d best of %d groups of %d experts for the top %d", keep, n_groups, n_experts, top);
     if (n_tok == 0) return 0;
-    const size_t smem = (size_t)4 * n_experts * sizeof(float);
-    moe_route_kernel<<<(n_tok + 3) / 4, 128, smem, (cudaStream_t)stream>>>(logits, n_tok, n_experts, top, ids, weights);
+    if (n_groups < 1) n_groups = 1;
+    const size_t smem = (size_t)4 * (n_experts + n_groups) * sizeof(float);
+    moe_route_kernel<<<(n_tok + 3) / 4, 128, smem, (cudaStream_t)stream>>>(logits, n_tok, n_experts, top, ids, weights,
+                                                                          all_scores, n_groups, keep, scale);
     NN_LAUNCH_OK("router");
     return 0;
 }
@@ -1986,7 +2068,7 @@ __device__ __forceinline__ float warp_dot(const void* __restrict__ w, size_t row
 __global__ void __launch_bounds__(256)
 moe_router_kernel(const void* __restrict__ x, int x_dt, const void* __restrict__ w, int w_dt, const void* __restrict__ bias,
                   int b_dt, int n_tok, int per_block, int n_experts, int top, int width, int* __restrict__ ids,
-                  float* __restrict__ weights) {
+                  float* __restrict__ weights, int all_scores, int n_groups, int keep, float scale) {
     extern __shared__ float smem[];          // a token's input, then its logits
     float* z = smem + width;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
@@ -1999,25 +2081,35 @@ moe_router_kernel(const void* __restrict__ x, int x_dt, const void* __restrict__
             if (lane == 0) z[e] = d + (bias ? ld_f(bias, e, b_dt) : 0.0f);
         }
         __syncthreads();
-        if (warp == 0) route_top(z, n_experts, top, ids + (size_t)t * top, weights + (size_t)t * top, lane);
+        if (warp == 0) {
+            if (all_scores)
+                route_top_all(z, z + n_experts, n_experts, top, n_groups, keep, scale, ids + (size_t)t * top,
+                              weights + (size_t)t * top, lane);
+            else
+                route_top(z, n_experts, top, ids + (size_t)t * top, weights + (size_t)t * top, lane);
+        }
         __syncthreads();
     }
 }
 
 extern "C" int nncpu_moe_router_fits(int n_experts, int width) {
-    return n_experts > 0 && n_experts <= kRouteMaxExperts && (size_t)(width + n_experts) * 4 <= 48 * 1024;
+    return n_experts > 0 && n_experts <= kRouteMaxExperts && (size_t)(width + 2 * n_experts) * 4 <= 48 * 1024;
 }
 
 extern "C" int nncpu_moe_router(const void* x, int x_dt, const void* w, int w_dt, const void* bias, int b_dt, int n_tok,
-                                int n_experts, int top, int width, int* ids, float* weights, void* stream) {
+                                int n_experts, int top, int width, int* ids, float* weights, int all_scores, int n_groups,
+                                int keep, float scale, void* stream) {
     NN_CHECK(n_tok >= 0 && width > 0 && top > 0 && top <= n_experts && nncpu_moe_router_fits(n_experts, width),
              "router: %d tokens of %d, the top %d of %d experts", n_tok, width, top, n_experts);
+    NN_CHECK(all_scores ? route_groups_ok(n_experts, top, n_groups, keep) : n_groups <= 1,
+             "router: the %d best of %d groups of %d experts for the top %d", keep, n_groups, n_experts, top);
     if (n_tok == 0) return 0;
+    if (n_groups < 1) n_groups = 1;
     // One token a block: with several a block the router's rows did not stay in L1 and the grid got too small
     // (2 048 tokens of 4 096 lanes, 16 experts: 88 us a launch with one token a block, 124 us with eight).
     const int per_block = 1;
-    moe_router_kernel<<<(n_tok + per_block - 1) / per_block, 256, (size_t)(width + n_experts) * 4, (cudaStream_t)stream>>>(
-        x, x_dt, w, w_dt, bias, b_dt, n_tok, per_block, n_experts, top, width, ids, weights);
+    moe_router_kernel<<<(n_tok + per_block - 1) / per_block, 256, (size_t)(width + n_experts + n_groups) * 4, (cudaStream_t)stream>>>(
+        x, x_dt, w, w_dt, bias, b_dt, n_tok, per_block, n_experts, top, width, ids, weights, all_scores, n_groups, keep, scale);
     NN_LAUNCH_OK("router");
     return 0;
 }
@@ -2222,5 +2314,211 @@ extern "C" int nncpu_moe_combine(const void* y, int y_dt, const int* row_of_slot
     NN_CHECK(n_tok > 0 && top > 0 && width > 0, "experts (combine): %d tokens of %d", n_tok, width);
     moe_combine_kernel<<<n_tok, 256, 0, (cudaStream_t)stream>>>(y, y_dt, row_of_slot, weights, out, top, width);
     NN_LAUNCH_OK("experts (combine)");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Layer norm over the last axis with weight and bias: y = (x - mean) / sqrt(var + eps) * w + b, where var is the
+// mean of the squared deviations from the mean (two passes: the mean first, then the deviations).  x float32;
+// `rows` (optional) picks input rows; a negative row gives zeros.  32-bit throughout.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+layernorm_kernel(const float* __restrict__ x, const void* __restrict__ w, const void* __restrict__ b, int p_dt,
+                 void* __restrict__ y, int y_dt, const int* __restrict__ rows, int dim, float eps) {
+    __shared__ float scratch[33];
+    const int r_out = blockIdx.x;
+    const int r_in = rows ? rows[r_out] : r_out;
+    if (r_in < 0) {
+        for (int i = threadIdx.x; i < dim; i += blockDim.x) st_f(y, (size_t)r_out * dim + i, y_dt, 0.0f);
+        return;
+    }
+    const float* src = x + (size_t)r_in * dim;
+    float s = 0.0f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) s += src[i];
+    const float mean = block_sum(s, scratch) * (1.0f / (float)dim);
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        const float c = src[i] - mean;
+        ss = fmaf(c, c, ss);
+    }
+    const float scale = 1.0f / sqrtf(block_sum(ss, scratch) * (1.0f / (float)dim) + eps);
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        float v = (src[i] - mean) * scale;
+        if (w) v *= ld_f(w, i, p_dt);
+        if (b) v += ld_f(b, i, p_dt);
+        st_f(y, (size_t)r_out * dim + i, y_dt, v);
+    }
+}
+
+extern "C" int nncpu_layernorm(const float* x, const void* w, const void* b, int p_dt, void* y, int y_dt,
+                               const int* rows, int n_rows, int dim, float eps, void* stream) {
+    NN_CHECK(n_rows >= 0 && dim > 0, "layernorm: %d rows of %d", n_rows, dim);
+    if (n_rows == 0) return 0;
+    layernorm_kernel<<<n_rows, 256, 0, (cudaStream_t)stream>>>(x, w, b, p_dt, y, y_dt, rows, dim, eps);
+    NN_LAUNCH_OK("layernorm");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// A hashed embedding of the pair (previous token, token): out[t, :] += table[row, :] with
+// row = (prev * mul_prev + id * mul_cur) mod buckets, and row = buckets (the table's last row) for a sequence's first
+// token.  The previous token of a step's first token is what `last` [slots + 1] holds for the sequence's slot; the
+// block of that token also leaves the sequence's last token of this step there (it is the only block that reads or
+// writes the slot's entry in the step).  A token of no sequence (tok_seq < 0) is left as it is.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+pair_embed_kernel(const void* __restrict__ table, int table_dt, const int* __restrict__ ids,
+                  const int* __restrict__ tok_seq, const int* __restrict__ tok_pos, const int* __restrict__ cu_seqlens,
+                  const int* __restrict__ seq_slots, int* last, float* __restrict__ out, int hidden, long long buckets,
+                  long long mul_prev, long long mul_cur) {
+    __shared__ int s_prev;
+    const int t = blockIdx.x;
+    const int seq = tok_seq[t];
+    if (seq < 0) return;
+    const int slot = seq_slots[seq];
+    if (slot < 0) return;
+    const int first = cu_seqlens[seq];
+    const int id = ids[t];
+    if (threadIdx.x == 0) {
+        if (t > first) {
+            s_prev = ids[t - 1];
+        } else {
+            s_prev = tok_pos[t] == 0 ? -1 : last[slot];
+            last[slot] = ids[cu_seqlens[seq + 1] - 1];
+        }
+    }
+    __syncthreads();
+    const int prev = s_prev;
+    const long long row = prev < 0 ? buckets : ((long long)prev * mul_prev + (long long)id * mul_cur) % buckets;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+        out[(size_t)t * hidden + i] += ld_f(table, (size_t)row * hidden + i, table_dt);
+}
+
+extern "C" int nncpu_pair_embed(const void* table, int table_dt, const int* ids, const int* tok_seq, const int* tok_pos,
+                                const int* cu_seqlens, const int* seq_slots, int* last, float* out, int n_tok,
+                                int hidden, long buckets, long mul_prev, long mul_cur, void* stream) {
+    NN_CHECK(n_tok >= 0 && hidden > 0 && buckets > 0 && mul_prev >= 0 && mul_cur >= 0,
+             "pair embedding: %d tokens of %d, %ld buckets", n_tok, hidden, buckets);
+    if (n_tok == 0) return 0;
+    pair_embed_kernel<<<n_tok, 256, 0, (cudaStream_t)stream>>>(table, table_dt, ids, tok_seq, tok_pos, cu_seqlens,
+                                                               seq_slots, last, out, hidden, buckets, mul_prev, mul_cur);
+    NN_LAUNCH_OK("pair embedding");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// out[t, :] = [a[t, :], b[t, :]] in the element type of out (b may be null: a plain conversion).  a, b float32.
+// ---------------------------------------------------------------------------
+__global__ void concat_rows_kernel(const float* __restrict__ a, const float* __restrict__ b, void* __restrict__ out,
+                                   int out_dt, long total, int dim) {
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int wide = b ? 2 * dim : dim;
+    const long t = idx / wide;
+    const int i = (int)(idx % wide);
+    st_f(out, (size_t)idx, out_dt, i < dim ? a[(size_t)t * dim + i] : b[(size_t)t * dim + i - dim]);
+}
+
+extern "C" int nncpu_concat_rows(const float* a, const float* b, void* out, int out_dt, int n_tok, int dim, void* stream) {
+    NN_CHECK(n_tok >= 0 && dim > 0, "concat: %d rows of %d", n_tok, dim);
+    if (n_tok == 0) return 0;
+    const long total = (long)n_tok * dim * (b ? 2 : 1);
+    concat_rows_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(a, b, out, out_dt, total, dim);
+    NN_LAUNCH_OK("concat");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// x[t, :] += alpha * y[t, :] (float32): a sublayer's branch joins the residual stream with a weight.
+// ---------------------------------------------------------------------------
+__global__ void stream_axpy_kernel(float* __restrict__ x, const float* __restrict__ y, float alpha, long total) {
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < total) x[idx] = fmaf(alpha, y[idx], x[idx]);
+}
+
+extern "C" int nncpu_stream_axpy(float* x, const float* y, float alpha, long total, void* stream) {
+    NN_CHECK(total >= 0, "axpy: %ld elements", total);
+    if (total == 0) return 0;
+    stream_axpy_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, y, alpha, total);
+    NN_LAUNCH_OK("axpy");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// x[t, :] += alpha * (a[t, :] / rms(a[t]) * wa + b[t, :] / rms(b[t]) * wb): one or two branches (b may be null), each
+// RMS-normed over the row (eps inside the root) with a plain weight (null: ones), join the residual stream.  32-bit.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+branch_norm_add_kernel(float* __restrict__ x, const float* __restrict__ a, const void* __restrict__ wa,
+                       const float* __restrict__ b, const void* __restrict__ wb, int w_dt, float eps, float alpha, int dim) {
+    __shared__ float scratch[33];
+    const size_t base = (size_t)blockIdx.x * dim;
+    float sa = 0.0f, sb = 0.0f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        const float va = a[base + i];
+        sa = fmaf(va, va, sa);
+        if (b) {
+            const float vb = b[base + i];
+            sb = fmaf(vb, vb, sb);
+        }
+    }
+    const float ra = 1.0f / sqrtf(block_sum(sa, scratch) * (1.0f / (float)dim) + eps);
+    const float rb = b ? 1.0f / sqrtf(block_sum(sb, scratch) * (1.0f / (float)dim) + eps) : 0.0f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        float v = (a[base + i] * ra) * (wa ? ld_f(wa, i, w_dt) : 1.0f);
+        if (b) v += (b[base + i] * rb) * (wb ? ld_f(wb, i, w_dt) : 1.0f);
+        x[base + i] = fmaf(alpha, v, x[base + i]);
+    }
+}
+
+extern "C" int nncpu_branch_norm_add(float* x, const float* a, const void* wa, const float* b, const void* wb, int w_dt,
+                                     float eps, float alpha, int n_tok, int dim, void* stream) {
+    NN_CHECK(n_tok >= 0 && dim > 0 && a != nullptr, "branch norm: %d rows of %d", n_tok, dim);
+    if (n_tok == 0) return 0;
+    branch_norm_add_kernel<<<n_tok, 256, 0, (cudaStream_t)stream>>>(x, a, wa, b, wb, w_dt, eps, alpha, dim);
+    NN_LAUNCH_OK("branch norm");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Elementwise activations of one product's 32-bit result: kind 0 the square of relu.
+// ---------------------------------------------------------------------------
+__global__ void unary_act_kernel(const float* __restrict__ x, void* __restrict__ out, int out_dt, long n, int kind) {
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n) return;
+    st_f(out, (size_t)idx, out_dt, plain_act_f(x[idx], kind == 0 ? kActRelu2 : kActNone, 0.0f, 0.0f));
+}
+
+extern "C" int nncpu_unary_act(const float* x, void* out, int out_dt, long n, int kind, void* stream) {
+    NN_CHECK(n >= 0 && kind == 0, "activation: %ld elements, kind %d", n, kind);
+    if (n == 0) return 0;
+    unary_act_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, out, out_dt, n, kind);
+    NN_LAUNCH_OK("activation");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// A token's own lanes gate a small projection: out[t, j] = gelu_tanh(z[t, j]) * table[ids[t], col + j], j < dim, with
+// `table` [vocab, ld] holding a part of `dim` lanes per layer.  z float32; a negative id gives zeros.
+// ---------------------------------------------------------------------------
+__global__ void token_gate_kernel(const float* __restrict__ z, const void* __restrict__ table, int table_dt,
+                                  const int* __restrict__ ids, int ld, int col, void* __restrict__ out, int out_dt,
+                                  long total, int dim) {
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const long t = idx / dim;
+    const int j = (int)(idx % dim), id = ids[t];
+    const float e = id >= 0 ? ld_f(table, (size_t)id * ld + col + j, table_dt) : 0.0f;
+    st_f(out, (size_t)idx, out_dt, gelu_tanh_f(z[idx]) * e);
+}
+
+extern "C" int nncpu_token_gate(const float* z, const void* table, int table_dt, const int* ids, int ld, int col,
+                                void* out, int out_dt, int n_tok, int dim, void* stream) {
+    NN_CHECK(n_tok >= 0 && dim > 0 && col >= 0 && col + dim <= ld, "token gate: lanes %d..%d of %d", col, col + dim, ld);
+    if (n_tok == 0) return 0;
+    const long total = (long)n_tok * dim;
+    token_gate_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(z, table, table_dt, ids, ld, col,
+                                                                                       out, out_dt, total, dim);
+    NN_LAUNCH_OK("token gate");
     return 0;
 }

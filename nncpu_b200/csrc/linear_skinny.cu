@@ -243,7 +243,7 @@ skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restri
                 for (int w = 0; w < kW; ++w) v += part[w][j][tok];
                 if (nf.bins_in != nullptr) v *= row_scale[tok];
                 if (bias) v += ld_f(bias, row, bias_dt);
-                if (nf.act == kActXielu) v = xielu_f(v, nf.act_a, nf.act_b);
+                if (nf.act == kActXielu || nf.act == kActRelu2) v = plain_act_f(v, nf.act, nf.act_a, nf.act_b);
                 if (accumulate) v += before[e];
                 st_f(out, (size_t)tok * ldc + row, out_dt, v);
             }
@@ -347,7 +347,7 @@ extern "C" int nncpu_linear_skinny(const void* X, const void* W, const void* bia
     const int n_out = epilogue == kSwiglu ? N / 2 : N;
     NN_CHECK(ldc >= n_out, "linear (few tokens): ldc %d is below the %d output features", ldc, n_out);
     NormFusion nf{};
-    NN_CHECK(act == kActNone || (act == kActXielu && epilogue == kPlain && !accumulate && xg_out == nullptr) ||
+    NN_CHECK(act == kActNone || ((act == kActXielu || act == kActRelu2) && epilogue == kPlain && !accumulate && xg_out == nullptr) ||
                  ((act == kActGateGelu || act == kActGateSwishClamp) && epilogue == kSwiglu),
              "linear (few tokens): activation %d goes with the plain epilogue (without accumulation or a norm after it) or, as a gate, with the gated one", act);
     nf.act = act; nf.act_a = act_a; nf.act_b = act_b;

@@ -68,7 +68,7 @@ template <int DMAX, int CPL>
 __global__ void __launch_bounds__(32 * kScanCols / CPL)
 gla_scan_kernel(const float* __restrict__ proj, int row, const float* __restrict__ z, float* __restrict__ state,
                 const int* __restrict__ seq_slots, const int* __restrict__ cu_seqlens, float* __restrict__ o, int H,
-                int d, int e, float q_scale, float inv_tau, int decays_given) {
+                int d, int e, float q_scale, float inv_tau, int decays_given, const float* __restrict__ head_decay) {
     constexpr int DR = DMAX / 32;                             // rows of its columns that a lane keeps
     constexpr int TB = DMAX <= 128 ? kScanGroup : DMAX <= 256 ? kScanGroup / 2 : kScanGroup / 4;   // tokens a group (shared memory: 2 TB DMAX 16 bytes)
     constexpr int kScanThreads = 32 * kScanCols / CPL;
@@ -112,7 +112,7 @@ gla_scan_kernel(const float* __restrict__ proj, int row, const float* __restrict
                 const float* p = proj + (size_t)(g0 + tt) * row;
                 nq[c] = p[q_at + i];
                 nk[c] = p[k_at + i];
-                nz[c] = z[(size_t)(g0 + tt) * H * d + (size_t)h * d + i];
+                nz[c] = head_decay ? head_decay[h] : z[(size_t)(g0 + tt) * H * d + (size_t)h * d + i];
             }
         }
         const int col = blockIdx.z * kScanCols + v_col;
@@ -201,7 +201,9 @@ extern "C" void nncpu_gla_scan_force_columns(int cpl) { g_scan_cpl = (cpl == 2 |
 
 extern "C" int nncpu_gla_scan(const float* proj, int row, const float* z, float* state, const int* seq_slots,
                               const int* cu_seqlens, float* o, int n_seqs, int H, int d, int e, float q_scale,
-                              float tau, int decays_given, void* stream) {
+                              float tau, int decays_given, const float* head_decay, void* stream) {
+    // head_decay [H] (optional): one fixed decay per head for every key channel and token; z is then not read
+    if (head_decay != nullptr) decays_given = 1;
     NN_CHECK(n_seqs >= 0 && H > 0 && d > 0 && e > 0, "gla_scan: %d sequences, %d heads of %d x %d", n_seqs, H, d, e);
     NN_CHECK(d <= 512, "gla_scan: %d key channels a head (at most 512)", d);
     NN_CHECK(row >= 2 * H * d + 2 * H * e, "gla_scan: rows of %d floats for %d heads of %d x %d", row, H, d, e);
@@ -222,10 +224,10 @@ extern "C" int nncpu_gla_scan(const float* proj, int row, const float* z, float*
     do {                                                                                                            \
         if (narrow)                                                                                                 \
             gla_scan_kernel<DMAX, 2><<<grid, 32 * kScanCols / 2, 0, st>>>(proj, row, z, state, seq_slots, cu_seqlens, o, H, d, \
-                                                                          e, q_scale, inv_tau, decays_given);      \
+                                                                          e, q_scale, inv_tau, decays_given, head_decay); \
         else                                                                                                        \
             gla_scan_kernel<DMAX, 4><<<grid, 32 * kScanCols / 4, 0, st>>>(proj, row, z, state, seq_slots, cu_seqlens, o, H, d, \
-                                                                          e, q_scale, inv_tau, decays_given);      \
+                                                                          e, q_scale, inv_tau, decays_given, head_decay); \
     } while (0)
     if (d <= 32) NN_SCAN(32);
     else if (d <= 64) NN_SCAN(64);
@@ -238,12 +240,13 @@ extern "C" int nncpu_gla_scan(const float* proj, int row, const float* z, float*
 }
 
 // The mixer's output stage: every head's o is divided by its root mean square over the e value channels (eps
-// inside the root), multiplied by the weight w [e] that the heads share and by silu(g), the gate of its channel.
+// inside the root), multiplied by the weight w [e] that the heads share (null: ones) and by silu(g), the gate of its
+// channel (gate_kind 1: by sigmoid(g)).
 // One warp per (token, head); out [n_tok, H*e] in the run's element type.
 __global__ void __launch_bounds__(256)
 gla_output_kernel(const float* __restrict__ o, const float* __restrict__ proj, int row, int g_at,
                   const void* __restrict__ w, int w_dt, float eps, void* __restrict__ out, int out_dt, long n_items,
-                  int H, int e) {
+                  int H, int e, int gate_kind) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long item = (long)blockIdx.x * 8 + warp;
     if (item >= n_items) return;
@@ -257,18 +260,19 @@ gla_output_kernel(const float* __restrict__ o, const float* __restrict__ proj, i
     const float* g = proj + (size_t)t * row + g_at + (size_t)h * e;
     for (int j = lane; j < e; j += 32) {
         const float gate = g[j];
-        const float y = (src[j] * scale) * ld_f(w, j, w_dt);
-        st_f(out, (size_t)t * H * e + (size_t)h * e + j, out_dt, y * (gate / (1.0f + expf(-gate))));
+        const float y = (src[j] * scale) * (w ? ld_f(w, j, w_dt) : 1.0f);
+        const float sg = 1.0f / (1.0f + expf(-gate));         // gate_kind 0: silu(gate), 1: sigmoid(gate)
+        st_f(out, (size_t)t * H * e + (size_t)h * e + j, out_dt, y * (gate_kind == 1 ? sg : gate * sg));
     }
 }
 
 extern "C" int nncpu_gla_output(const float* o, const float* proj, int row, int g_at, const void* w, int w_dt,
-                                float eps, void* out, int out_dt, int n_tok, int H, int e, void* stream) {
+                                float eps, void* out, int out_dt, int n_tok, int H, int e, int gate_kind, void* stream) {
     NN_CHECK(n_tok >= 0 && H > 0 && e > 0 && g_at >= 0 && g_at + H * e <= row, "gla_output: sizes");
     if (n_tok == 0) return 0;
     const long n_items = (long)n_tok * H;
     gla_output_kernel<<<(unsigned)((n_items + 7) / 8), 256, 0, (cudaStream_t)stream>>>(o, proj, row, g_at, w, w_dt, eps,
-                                                                                       out, out_dt, n_items, H, e);
+                                                                                       out, out_dt, n_items, H, e, gate_kind);
     NN_LAUNCH_OK("gla_output");
     return 0;
 }
@@ -282,7 +286,8 @@ template <int kThreads, int kInFlight>
 __global__ void __launch_bounds__(kThreads)
 gla_step_kernel(const float* __restrict__ proj, int row, const float* __restrict__ z, float* __restrict__ state,
                 const int* __restrict__ seq_slots, const void* __restrict__ w, int w_dt, float eps,
-                void* __restrict__ out, int out_dt, int H, int d, int e, float q_scale, float inv_tau) {
+                void* __restrict__ out, int out_dt, int H, int d, int e, float q_scale, float inv_tau,
+                const float* __restrict__ head_decay) {
     extern __shared__ float4 akq[];          // d entries of (a, k, q, -)
     __shared__ float scratch[33];
     const int t = blockIdx.x, h = blockIdx.y, j = threadIdx.x;
@@ -294,7 +299,7 @@ gla_step_kernel(const float* __restrict__ proj, int row, const float* __restrict
     }
     const float* p = proj + (size_t)t * row;
     for (int i = j; i < d; i += blockDim.x)
-        akq[i] = make_float4(expf(log_sigmoid_f(z[(size_t)t * H * d + (size_t)h * d + i]) * inv_tau),
+        akq[i] = make_float4(head_decay ? head_decay[h] : expf(log_sigmoid_f(z[(size_t)t * H * d + (size_t)h * d + i]) * inv_tau),
                              p[(size_t)H * d + (size_t)h * d + i], p[(size_t)h * d + i] * q_scale, 0.0f);
     __syncthreads();
     float acc = 0.0f;
@@ -327,13 +332,13 @@ gla_step_kernel(const float* __restrict__ proj, int row, const float* __restrict
     if (j < e) {
         const float scale = 1.0f / sqrtf(ss * (1.0f / (float)e) + eps);
         const float gate = p[2 * (size_t)H * d + (size_t)H * e + (size_t)h * e + j];
-        st_f(out, out_at, out_dt, ((acc * scale) * ld_f(w, j, w_dt)) * (gate / (1.0f + expf(-gate))));
+        st_f(out, out_at, out_dt, ((acc * scale) * (w ? ld_f(w, j, w_dt) : 1.0f)) * (gate / (1.0f + expf(-gate))));
     }
 }
 
 extern "C" int nncpu_gla_step(const float* proj, int row, const float* z, float* state, const int* seq_slots,
                               const void* w, int w_dt, float eps, void* out, int out_dt, int n_tok, int H, int d, int e,
-                              float q_scale, float tau, void* stream) {
+                              float q_scale, float tau, const float* head_decay, void* stream) {
     NN_CHECK(n_tok >= 0 && H > 0 && H <= 65535 && d > 0 && e > 0, "gla_step: %d tokens, %d heads of %d x %d", n_tok, H, d, e);
     NN_CHECK(e <= 1024, "gla_step: %d value channels a head (at most 1024)", e);
     NN_CHECK(d <= 2048, "gla_step: %d key channels a head (at most 2048)", d);
@@ -349,14 +354,55 @@ extern "C" int nncpu_gla_step(const float* proj, int row, const float* z, float*
     // fill the waits (batch 8 of 8 heads 20 -> 11 us with 32; batch 64 of 16 heads 57 us with 8, 78 with 32)
     if (threads <= 256 && (long)n_tok * H <= 2L * sms)
         gla_step_kernel<256, 32><<<dim3(n_tok, H), threads, (size_t)d * sizeof(float4), (cudaStream_t)stream>>>(
-            proj, row, z, state, seq_slots, w, w_dt, eps, out, out_dt, H, d, e, q_scale, 1.0f / tau);
+            proj, row, z, state, seq_slots, w, w_dt, eps, out, out_dt, H, d, e, q_scale, 1.0f / tau, head_decay);
     else if (threads <= 256)
         gla_step_kernel<256, 8><<<dim3(n_tok, H), threads, (size_t)d * sizeof(float4), (cudaStream_t)stream>>>(
-            proj, row, z, state, seq_slots, w, w_dt, eps, out, out_dt, H, d, e, q_scale, 1.0f / tau);
+            proj, row, z, state, seq_slots, w, w_dt, eps, out, out_dt, H, d, e, q_scale, 1.0f / tau, head_decay);
     else
         gla_step_kernel<1024, 8><<<dim3(n_tok, H), threads, (size_t)d * sizeof(float4), (cudaStream_t)stream>>>(
-            proj, row, z, state, seq_slots, w, w_dt, eps, out, out_dt, H, d, e, q_scale, 1.0f / tau);
+            proj, row, z, state, seq_slots, w, w_dt, eps, out, out_dt, H, d, e, q_scale, 1.0f / tau, head_decay);
     NN_LAUNCH_OK("gla_step");
+    return 0;
+}
+
+// Retention: linear attention with ONE fixed decay per head, S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t: the
+// recurrence of gated linear attention with a constant in place of the per-channel decays (gla_scan and gla_step take
+// `head_decay`).  What comes before it: q and k of every head are rotated by the token's position (the pairs (i, i +
+// half) of a head's first 2 half lanes by the table's (cos, sin) [n_tok, half, 2]; the rest pass), then k is
+// multiplied by k_scale.  In place, on the rows of proj [n_tok, row] that hold q (H d) and then k (H d).
+__global__ void __launch_bounds__(256)
+retention_prepare_kernel(float* __restrict__ proj, int row, const float* __restrict__ cos_sin, int half, long total,
+                         int H, int d, float k_scale) {
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int i = (int)(idx % d);
+    const long th = idx / d;
+    const int h = (int)(th % H);
+    const long t = th / H;
+    float* q = proj + (size_t)t * row + (size_t)h * d;
+    float* k = q + (size_t)H * d;
+    if (i < half) {
+        const float c = cos_sin[((size_t)t * half + i) * 2], sn = cos_sin[((size_t)t * half + i) * 2 + 1];
+        const float qu = q[i], qv = q[i + half], ku = k[i], kv = k[i + half];
+        q[i] = qu * c - qv * sn;
+        q[i + half] = qv * c + qu * sn;
+        k[i] = (ku * c - kv * sn) * k_scale;
+        k[i + half] = (kv * c + ku * sn) * k_scale;
+    } else if (i >= 2 * half) {
+        k[i] *= k_scale;
+    }
+}
+
+extern "C" int nncpu_retention_prepare(float* proj, int row, const float* cos_sin, int half, int n_tok, int H, int d,
+                                       float k_scale, void* stream) {
+    NN_CHECK(n_tok >= 0 && H > 0 && d > 0 && half >= 0 && 2 * half <= d && row >= 2 * H * d,
+             "retention: %d heads of %d lanes, %d of them rotated, rows of %d", H, d, 2 * half, row);
+    NN_CHECK(half == 0 || cos_sin != nullptr, "retention: a rotation without its table");
+    if (n_tok == 0) return 0;
+    const long total = (long)n_tok * H * d;
+    retention_prepare_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(proj, row, cos_sin, half,
+                                                                                             total, H, d, k_scale);
+    NN_LAUNCH_OK("retention prepare");
     return 0;
 }
 
@@ -391,7 +437,7 @@ delta_prepare_kernel(const float* __restrict__ proj, int ld, const void* __restr
                      const int* __restrict__ seq_slots, const int* __restrict__ cu_seqlens,
                      const void* __restrict__ a_log, const void* __restrict__ dt_bias, int p_dt,
                      float* __restrict__ xc, float* __restrict__ gb, long n_items, int H, int G, int d, int e, int taps,
-                     float q_scale) {
+                     float q_scale, int beta_col, float* __restrict__ chan_z) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long item = (long)blockIdx.x * 8 + warp;
     if (item >= n_items) return;
@@ -404,12 +450,17 @@ delta_prepare_kernel(const float* __restrict__ proj, int ld, const void* __restr
         for (int h = lane; h < H; h += 32) {
             float g = 0.0f, beta = 0.0f;
             if (slot >= 0) {
-                const float* p = proj + (size_t)t * ld + C + (size_t)H * e;
+                const float* p = proj + (size_t)t * ld + beta_col;
                 beta = 1.0f / (1.0f + expf(0.0f - p[h]));
-                g = expf(0.0f - expf(ld_f(a_log, h, p_dt)) * softplus_r(p[H + h] + ld_f(dt_bias, h, p_dt)));
+                g = chan_z ? 1.0f : expf(0.0f - expf(ld_f(a_log, h, p_dt)) * softplus_r(p[H + h] + ld_f(dt_bias, h, p_dt)));
             }
             gb[(size_t)t * 2 * H + h] = g;
             gb[(size_t)t * 2 * H + H + h] = beta;
+        }
+        if (chan_z) {       // a decay per head and key channel, from its logit (the bias is in it already), in place
+            float* zz = chan_z + (size_t)t * H * d;
+            for (int i = lane; i < H * d; i += 32)
+                zz[i] = slot >= 0 ? expf(0.0f - expf(ld_f(a_log, i / d, p_dt)) * softplus_r(zz[i])) : 0.0f;
         }
         return;
     }
@@ -471,22 +522,25 @@ delta_conv_state_kernel(const float* __restrict__ proj, int ld, float* __restric
 extern "C" int nncpu_delta_prepare(const float* proj, int ld, const void* conv_w, int w_dt, float* conv_state,
                                    long slot_stride, const int* tok_seq, const int* seq_slots, const int* cu_seqlens, const void* a_log,
                                    const void* dt_bias, int p_dt, float* xc, float* gb, int n_tok, int n_seqs, int H,
-                                   int G, int d, int e, int taps, float q_scale, int one_token_each, void* stream) {
+                                   int G, int d, int e, int taps, float q_scale, int one_token_each, int beta_col,
+                                   float* chan_z, void* stream) {
+    // beta_col: where a row of proj holds the H logits of beta (the H decay inputs follow them unless chan_z is given:
+    // float [n_tok, H d] logits of a decay per head and key channel, turned into the decays in place)
     NN_CHECK(n_tok >= 0 && n_seqs >= 0 && H > 0 && G > 0 && H % G == 0 && d > 0 && e > 0,
              "delta prepare: %d heads over %d query/key heads of %d x %d", H, G, d, e);
     NN_CHECK(taps >= 1 && taps <= kMaxTaps, "delta prepare: %d taps (1 to %d)", taps, kMaxTaps);
     const int C = 2 * G * d + H * e;
-    NN_CHECK(ld >= C + H * e + 2 * H, "delta prepare: rows of %d floats", ld);
+    NN_CHECK(beta_col >= C && ld >= beta_col + (chan_z ? 1 : 2) * H, "delta prepare: rows of %d floats", ld);
     if (n_tok == 0) return 0;
     const long n_items = (long)n_tok * (2 * G + H + 1);
     if (one_token_each)
         delta_prepare_kernel<true><<<(unsigned)((n_items + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
             proj, ld, conv_w, w_dt, conv_state, slot_stride, tok_seq, seq_slots, cu_seqlens, a_log, dt_bias, p_dt, xc, gb, n_items, H,
-            G, d, e, taps, q_scale);
+            G, d, e, taps, q_scale, beta_col, chan_z);
     else
         delta_prepare_kernel<false><<<(unsigned)((n_items + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
             proj, ld, conv_w, w_dt, conv_state, slot_stride, tok_seq, seq_slots, cu_seqlens, a_log, dt_bias, p_dt, xc, gb, n_items, H,
-            G, d, e, taps, q_scale);
+            G, d, e, taps, q_scale, beta_col, chan_z);
     NN_LAUNCH_OK("delta prepare");
     if (taps > 1 && n_seqs > 0 && !one_token_each) {
         const long total = (long)n_seqs * C;
@@ -515,17 +569,25 @@ __device__ __forceinline__ void cp_async_wait_one_() { asm volatile("cp.async.wa
 // g and beta of a group of tokens are staged in shared memory by asynchronous copies, the next group's in flight under
 // this group's arithmetic.  The order of operations of a (sequence, head, column) does not depend on how the sequence
 // was cut into steps or on what else the step holds.  A negative slot (padding): zeros out, no state touched.
-template <int DR, int R, int CPL>
+// Tokens a group: what two buffers of the default shared memory hold.  With a decay per key channel (CH) a buffer
+// also holds the tokens' decays.
+__host__ __device__ constexpr int delta_group(int DP, bool CH) {
+    return CH ? (DP <= 128 ? 8 : DP <= 256 ? 4 : DP <= 512 ? 2 : 1) : (DP <= 256 ? 8 : (DP <= 512 ? 4 : 2));
+}
+
+// CH: the decay is one number per head and key channel (gch [n_tok, H d]), S <- diag(g) S, instead of one per head.
+template <int DR, int R, int CPL, bool CH>
 __global__ void __launch_bounds__(128)
-delta_scan_kernel(const float* __restrict__ xc, const float* __restrict__ gb, float* __restrict__ state,
+delta_scan_kernel(const float* __restrict__ xc, const float* __restrict__ gb, const float* __restrict__ gch,
+                  float* __restrict__ state,
                   long slot_stride, const int* __restrict__ seq_slots, const int* __restrict__ cu_seqlens, float* __restrict__ o, int H,
                   int G, int d, int e) {
     static_assert(DR % 4 == 0, "a lane keeps whole groups of four rows");
     constexpr int DP = DR * R;                      // rows the lanes cover (>= d; the rest hold zeros)
     constexpr int CW = CPL * 32 / R;                // columns a warp: CPL neighbouring ones a lane
     constexpr int COLS = 4 * CW;                    // columns a block
-    constexpr int TB = DP <= 256 ? 8 : (DP <= 512 ? 4 : 2);       // tokens a group
-    constexpr int BUF = TB * (2 * DP + COLS + 2);   // floats a buffer: k, q [TB][DP], v [TB][COLS], (g, beta) [TB]
+    constexpr int TB = delta_group(DP, CH);         // tokens a group
+    constexpr int BUF = TB * ((CH ? 3 : 2) * DP + COLS + 2);   // floats a buffer: k, q (, decays) [TB][DP], v [TB][COLS], (g, beta) [TB]
     extern __shared__ __align__(16) float dsm_[];
     const int seq = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31, r = lane % R;
@@ -561,6 +623,22 @@ delta_scan_kernel(const float* __restrict__ xc, const float* __restrict__ gb, fl
         float* qb = kb + TB * DP;
         float* vb = qb + TB * DP;
         float* gbb = vb + TB * COLS;
+        if (CH) {
+            float* gcb = gbb + TB * 2;
+            const bool wide_g = (d & 3) == 0 && (reinterpret_cast<uintptr_t>(gch) & 15) == 0;
+            if (wide_g) {
+                const int d4 = d >> 2;
+                for (int idx = tid; idx < nt * d4; idx += 128) {
+                    const int tt = idx / d4, i = (idx % d4) << 2;
+                    cp_async16_(gcb + tt * DP + i, gch + ((size_t)(g0 + tt) * H + h) * d + i);
+                }
+            } else {
+                for (int idx = tid; idx < nt * d; idx += 128) {
+                    const int tt = idx / d, i = idx % d;
+                    cp_async4(gcb + tt * DP + i, gch + ((size_t)(g0 + tt) * H + h) * d + i);
+                }
+            }
+        }
         if (wide) {          // rows of xc start on 16-byte borders, and so do the heads in them
             const int d4 = d >> 2;
             for (int idx = tid; idx < nt * d4; idx += 128) {
@@ -599,6 +677,7 @@ delta_scan_kernel(const float* __restrict__ xc, const float* __restrict__ gb, fl
         const float* qb = kb + TB * DP;
         const float* vb = qb + TB * DP;
         const float* gbb = vb + TB * COLS;
+        const float* gcb = gbb + TB * 2;             // (CH) the tokens' decays per key channel
         // One token: the chain from token to token is S^T k (DR multiply-adds in four sums, log2(R) shuffles), u, and
         // the update of S, once per column of the lane: the lane's columns are independent chains that share the
         // loads of k and q and fill one another's waits.  The lane's parts of o = S^T q are left in os; their sums
@@ -613,10 +692,19 @@ delta_scan_kernel(const float* __restrict__ xc, const float* __restrict__ gb, fl
             for (int c = 0; c < DR / 4; ++c) {
                 const float4 k4 = *reinterpret_cast<const float4*>(kb + tt * DP + (c * R + r) * 4);
                 kk[4 * c] = k4.x; kk[4 * c + 1] = k4.y; kk[4 * c + 2] = k4.z; kk[4 * c + 3] = k4.w;
+                if (CH) {        // S^T k of the decayed state: the rows' decays go with k
+                    const float4 g4 = *reinterpret_cast<const float4*>(gcb + tt * DP + (c * R + r) * 4);
+                    const float kg[4] = {k4.x * g4.x, k4.y * g4.y, k4.z * g4.z, k4.w * g4.w};
 #pragma unroll
-                for (int cc = 0; cc < CPL; ++cc)
+                    for (int cc = 0; cc < CPL; ++cc)
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) p[cc][j] = fmaf(kk[4 * c + j], S[cc][4 * c + j], p[cc][j]);
+                        for (int j = 0; j < 4; ++j) p[cc][j] = fmaf(kg[j], S[cc][4 * c + j], p[cc][j]);
+                } else {
+#pragma unroll
+                    for (int cc = 0; cc < CPL; ++cc)
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) p[cc][j] = fmaf(kk[4 * c + j], S[cc][4 * c + j], p[cc][j]);
+                }
             }
             float ks[CPL], u[CPL];
 #pragma unroll
@@ -635,11 +723,16 @@ delta_scan_kernel(const float* __restrict__ xc, const float* __restrict__ gb, fl
             for (int c = 0; c < DR / 4; ++c) {
                 const float4 q4 = *reinterpret_cast<const float4*>(qb + tt * DP + (c * R + r) * 4);
                 const float qq[4] = {q4.x, q4.y, q4.z, q4.w};
+                float gg[4] = {g, g, g, g};
+                if (CH) {
+                    const float4 g4 = *reinterpret_cast<const float4*>(gcb + tt * DP + (c * R + r) * 4);
+                    gg[0] = g4.x; gg[1] = g4.y; gg[2] = g4.z; gg[3] = g4.w;
+                }
 #pragma unroll
                 for (int cc = 0; cc < CPL; ++cc)
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        S[cc][4 * c + j] = fmaf(g, S[cc][4 * c + j], kk[4 * c + j] * u[cc]);
+                        S[cc][4 * c + j] = fmaf(gg[j], S[cc][4 * c + j], kk[4 * c + j] * u[cc]);
                         a[cc][j] = fmaf(qq[j], S[cc][4 * c + j], a[cc][j]);
                     }
             }
@@ -692,13 +785,17 @@ delta_scan_kernel(const float* __restrict__ xc, const float* __restrict__ gb, fl
 }
 
 template <int DR, int R, int CPL>
-static int launch_delta_scan(const float* xc, const float* gb, float* state, long slot_stride, const int* seq_slots, const int* cu_seqlens,
+static int launch_delta_scan(const float* xc, const float* gb, const float* gch, float* state, long slot_stride, const int* seq_slots, const int* cu_seqlens,
                              float* o, int n_seqs, int H, int G, int d, int e, cudaStream_t st) {
-    constexpr int DP = DR * R, COLS = 4 * (CPL * 32 / R), TB = DP <= 256 ? 8 : (DP <= 512 ? 4 : 2);
-    constexpr size_t smem = (size_t)2 * TB * (2 * DP + COLS + 2) * sizeof(float);
-    static_assert(smem <= 48 * 1024, "the staging buffers fit the default shared memory");
+    constexpr int DP = DR * R, COLS = 4 * (CPL * 32 / R);
+    constexpr size_t smem = (size_t)2 * delta_group(DP, false) * (2 * DP + COLS + 2) * sizeof(float);
+    constexpr size_t smem_ch = (size_t)2 * delta_group(DP, true) * (3 * DP + COLS + 2) * sizeof(float);
+    static_assert(smem <= 48 * 1024 && smem_ch <= 48 * 1024, "the staging buffers fit the default shared memory");
     dim3 grid(n_seqs, H, (e + COLS - 1) / COLS);
-    delta_scan_kernel<DR, R, CPL><<<grid, 128, smem, st>>>(xc, gb, state, slot_stride, seq_slots, cu_seqlens, o, H, G, d, e);
+    if (gch != nullptr)
+        delta_scan_kernel<DR, R, CPL, true><<<grid, 128, smem_ch, st>>>(xc, gb, gch, state, slot_stride, seq_slots, cu_seqlens, o, H, G, d, e);
+    else
+        delta_scan_kernel<DR, R, CPL, false><<<grid, 128, smem, st>>>(xc, gb, gch, state, slot_stride, seq_slots, cu_seqlens, o, H, G, d, e);
     return 0;
 }
 
@@ -709,8 +806,9 @@ static int g_delta_cpl = 0;      // and of the columns a lane (0: the rule below
 extern "C" void nncpu_delta_scan_force_lanes(int lanes) { g_delta_lanes = lanes; }
 extern "C" void nncpu_delta_scan_force_columns(int cpl) { g_delta_cpl = cpl; }
 
-extern "C" int nncpu_delta_scan(const float* xc, const float* gb, float* state, long slot_stride, const int* seq_slots,
+extern "C" int nncpu_delta_scan(const float* xc, const float* gb, const float* gch, float* state, long slot_stride, const int* seq_slots,
                                 const int* cu_seqlens, float* o, int n_seqs, int H, int G, int d, int e, void* stream) {
+    // gch (optional): float [n_tok, H d], a decay per head and key channel; the per-head decays of gb are then not used
     NN_CHECK(n_seqs >= 0 && H > 0 && G > 0 && H % G == 0 && d > 0 && e > 0, "delta scan: %d sequences, %d heads of %d x %d",
              n_seqs, H, d, e);
     NN_CHECK(d <= 1024, "delta scan: %d key channels a head (at most 1024)", d);
@@ -738,9 +836,9 @@ extern "C" int nncpu_delta_scan(const float* xc, const float* gb, float* state, 
     if (CPL == 2) R *= 2;
 #define NN_DELTA(DP_, R_)                                                                                              \
     if (DP == DP_ && R == R_ && CPL == 1)                                                                              \
-        launch_delta_scan<DP_ / R_, R_, 1>(xc, gb, state, slot_stride, seq_slots, cu_seqlens, o, n_seqs, H, G, d, e, st); \
+        launch_delta_scan<DP_ / R_, R_, 1>(xc, gb, gch, state, slot_stride, seq_slots, cu_seqlens, o, n_seqs, H, G, d, e, st); \
     if (DP == DP_ && R == R_ && CPL == 2)                                                                              \
-        launch_delta_scan<DP_ / R_, R_, 2>(xc, gb, state, slot_stride, seq_slots, cu_seqlens, o, n_seqs, H, G, d, e, st);
+        launch_delta_scan<DP_ / R_, R_, 2>(xc, gb, gch, state, slot_stride, seq_slots, cu_seqlens, o, n_seqs, H, G, d, e, st);
     NN_DELTA(32, 4) NN_DELTA(32, 8)
     NN_DELTA(64, 4) NN_DELTA(64, 8) NN_DELTA(64, 16)
     NN_DELTA(128, 4) NN_DELTA(128, 8) NN_DELTA(128, 16) NN_DELTA(128, 32)

@@ -66,6 +66,16 @@ def _injected_tables(spec: ModelSpec) -> Dict[str, int]:
     return tables
 
 
+def _mix_matrices(spec: ModelSpec) -> List[str]:
+    """Tensors [hidden, 2 hidden] that the schedule multiplies the pair (stream, embedding output) with
+    (``StreamInjection.mix``)."""
+    names: List[str] = []
+    for e in spec.schedule:
+        if e.inject is not None and e.inject.mix is not None and e.inject.mix not in names:
+            names.append(e.inject.mix)
+    return names
+
+
 def build_blocks(spec: ModelSpec) -> list:
     shares = _shares(spec)
     return [build("block", b, **({"reads_other_cache": True} if shares[i] else {}))
@@ -78,10 +88,19 @@ def parameter_list(spec: ModelSpec) -> List[ParamSpec]:
     params = [ParamSpec(e.name + e.suffix, (e.vocab_size, e.hidden_size))]
     if e.positions is not None:
         params.append(ParamSpec(e.positions, (e.n_positions, e.hidden_size)))
+    if e.pair_table is not None:
+        params.append(ParamSpec(e.pair_table, (e.pair_buckets + 1, e.hidden_size)))
+    for name in _mix_matrices(spec):
+        params.append(ParamSpec(name, (spec.hidden_size, 2 * spec.hidden_size)))
     for table, n_rows in _injected_tables(spec).items():
         params.append(ParamSpec(table, (n_rows, spec.hidden_size), init=("normal", 0.5)))
+    side_tables = set()
     for block in build_blocks(spec):
         params += block.params()
+        side = getattr(block, "side", None)     # a table of per-token lanes that all layers share is listed once
+        if side is not None and side.spec.table not in side_tables:
+            side_tables.add(side.spec.table)
+            params.append(side.table_param())
     params += build("norm", o.norm).params()
     if not o.tied:
         params.append(ParamSpec(o.name + o.suffix, (o.vocab_size, o.hidden_size)))
@@ -106,7 +125,11 @@ class Model:
         # what the schedule adds to the stream before some of its entries: rows of learned tables, and the stream as
         # the embedding left it (kept for the step only if some entry asks for it)
         self.injected = {name: tensors[name] for name in _injected_tables(spec)}
-        self.keeps_embedding = any(e.inject is not None and e.inject.embedding for e in spec.schedule)
+        self.mixes = {name: tensors[name] for name in _mix_matrices(spec)}
+        self.keeps_embedding = any(e.inject is not None and (e.inject.embedding or e.inject.mix is not None)
+                                   for e in spec.schedule)
+        # a hashed embedding of (previous token, token): the table, and a sequence's last token as per-sequence state
+        self.pair_table = None if spec.embedding.pair_table is None else tensors[spec.embedding.pair_table]
         for block in self.blocks:
             block.bind(tensors, rt)
         self.final_norm.bind(tensors, rt)
@@ -158,6 +181,12 @@ class Model:
             for k, (kv, state) in enumerate(asked):
                 requests.append((None if e.cache_of is not None else kv, state))
                 cache_of.append(None if e.cache_of is None else self._users[e.cache_of][0] + k)
+        self._embed_user = None
+        if self.spec.embedding.pair_table is not None:
+            # the embedding is a cache user of its own: one int32 per sequence, the last token it has seen
+            self._embed_user = len(requests)
+            requests.append((None, StateRequest((1,), torch.int32)))
+            cache_of.append(None)
         return requests, cache_of
 
     # -- numbers for reports ------------------------------------------------------
@@ -191,11 +220,18 @@ class Model:
         residual = rt.empty(ctx.n_tokens, spec.hidden_size, dtype=torch.float32)
         with rt.phase("embed"):
             ops.embed(self.embed_table, ctx.tok_ids, residual, spec.embedding.scale, self.pos_table, ctx.tok_pos)
+            if self.pair_table is not None:
+                e = spec.embedding
+                ops.pair_embed(self.pair_table, ctx.tok_ids, ctx.tok_seq, ctx.tok_pos, ctx.cu_seqlens, ctx.seq_slots,
+                               cache.state(self._embed_user), residual, e.pair_buckets, e.pair_mul_prev, e.pair_mul_cur)
         first_stream = None
         if self.keeps_embedding:
             first_stream = rt.empty(ctx.n_tokens, spec.hidden_size, dtype=torch.float32, keep=True)
             with rt.phase("embed"):
-                ops.embed(self.embed_table, ctx.tok_ids, first_stream, spec.embedding.scale, self.pos_table, ctx.tok_pos)
+                if self.pair_table is not None:     # the pair embedding advances its state: made once, then copied
+                    ops.concat_rows(residual, None, first_stream)
+                else:
+                    ops.embed(self.embed_table, ctx.tok_ids, first_stream, spec.embedding.scale, self.pos_table, ctx.tok_pos)
         ctx.next_norm = ctx.after_block = None
         fusing = rt.dtype == torch.bfloat16 and rt.fuses_norms(ctx.n_tokens, spec.hidden_size)
         if fusing:
@@ -203,9 +239,18 @@ class Model:
         for i, (e, (first, count)) in enumerate(zip(self.schedule, self._users)):
             if e.inject is not None:
                 ctx.next_norm = None            # the stream changes before the block's first norm reads it
-                with rt.phase("embed"):
-                    ops.stream_add(residual, first_stream if e.inject.embedding else None,
-                                   None if e.inject.table is None else self.injected[e.inject.table][e.inject.row])
+                row = None if e.inject.table is None else self.injected[e.inject.table][e.inject.row]
+                if e.inject.mix is not None:
+                    # the stream becomes W_mix [x; x0] (+ the table's row, as the product's bias)
+                    w_mix = self.mixes[e.inject.mix]
+                    with rt.scope(), rt.phase("stream_mix", w_mix, ctx.n_tokens):
+                        pair = rt.empty(ctx.n_tokens, 2 * spec.hidden_size)
+                        ops.concat_rows(residual, first_stream, pair)
+                        rt.linear(pair, w_mix, row, residual)
+                    row = None
+                if e.inject.embedding or row is not None:
+                    with rt.phase("embed"):
+                        ops.stream_add(residual, first_stream if e.inject.embedding else None, row)
             if i + 1 < len(self.schedule) and self.schedule[i + 1].inject is None:
                 # the block that follows may ask this one to leave its first norm's input (a few tokens only)
                 ctx.after_block = self.blocks[self.schedule[i + 1].layer].entry_norm_request(ctx, residual)

@@ -46,6 +46,7 @@ class StepContext:
     next_norm: Optional[object] = None    # a NormRequest for the part that is running: see parts.base.NormRequest
     after_block: Optional[object] = None  # the request of the block that follows, for the running block's last part
     branch_is_fresh: bool = False         # the "residual" a part was given is an uninitialised branch: its last product writes, not adds
+    out_scale: float = 1.0                # a part that says ``scales_output`` multiplies what it adds to the stream by this
 
     def span_sum(self, window: int = 0, chunk: int = 0) -> int:
         """Keys that the step's tokens attend to, summed over the tokens: a token at position p sees p + 1

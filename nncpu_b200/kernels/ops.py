@@ -148,6 +148,76 @@ def rmsnorm(x, gamma, eps: float, out, rows=None, gamma_offset: float = 0.0, acc
           _i(_code(out)), _ptr(rows), _i(n_rows), _i(dim), _f(eps), _f(gamma_offset), _i(accumulate), _stream())
 
 
+def layernorm(x, weight, bias, eps: float, out, rows=None) -> None:
+    """out = (x - mean) / sqrt(var + eps) * weight + bias per row, var the mean of the squared deviations; x float32,
+    32-bit arithmetic.  ``rows`` (int32) picks the input rows."""
+    n = out.shape[0]
+    dim = x.shape[1]
+    assert x.dtype == torch.float32 and x.is_contiguous() and out.shape == (n, dim)
+    assert weight.numel() == dim and bias.numel() == dim and weight.dtype == bias.dtype
+    assert rows is None or (rows.dtype == torch.int32 and rows.numel() == n)
+    _call("generic", "nncpu_layernorm", _ptr(x), _ptr(weight), _ptr(bias), _i(_code(weight)), _ptr(out), _i(_code(out)),
+          _ptr(rows), _i(n), _i(dim), _f(eps), _stream())
+
+
+def pair_embed(table, ids, tok_seq, tok_pos, cu_seqlens, seq_slots, last, out, buckets: int, mul_prev: int,
+               mul_cur: int) -> None:
+    """out[t] += table[(prev * mul_prev + id * mul_cur) mod buckets] with prev the token before token t in its
+    sequence, and table[buckets] for a sequence's first token.  ``last`` int32 [slots + 1, 1] holds every sequence's
+    last token from step to step: it is read for a step's first tokens and left at the step's last ones."""
+    n, hidden = out.shape
+    assert out.dtype == torch.float32 and out.is_contiguous() and table.shape == (buckets + 1, hidden)
+    assert ids.dtype == tok_seq.dtype == tok_pos.dtype == cu_seqlens.dtype == seq_slots.dtype == torch.int32
+    assert last.dtype == torch.int32 and last.is_contiguous() and ids.numel() >= n
+    _call("generic", "nncpu_pair_embed", _ptr(table), _i(_code(table)), _ptr(ids), _ptr(tok_seq), _ptr(tok_pos),
+          _ptr(cu_seqlens), _ptr(seq_slots), _ptr(last), _ptr(out), _i(n), _i(hidden), _l(buckets), _l(mul_prev),
+          _l(mul_cur), _stream())
+
+
+def concat_rows(a, b, out) -> None:
+    """out = [a, b] along the last axis in ``out``'s element type (``b`` None: a conversion of ``a``); a, b float32."""
+    n, dim = a.shape
+    assert a.dtype == torch.float32 and a.is_contiguous() and out.is_contiguous()
+    assert b is None or (b.dtype == torch.float32 and b.shape == a.shape and b.is_contiguous())
+    assert out.shape == (n, dim * (1 if b is None else 2))
+    _call("generic", "nncpu_concat_rows", _ptr(a), _ptr(b), _ptr(out), _i(_code(out)), _i(n), _i(dim), _stream())
+
+
+def stream_axpy(x, y, alpha: float) -> None:
+    """x += alpha * y, float32."""
+    assert x.dtype == y.dtype == torch.float32 and x.shape == y.shape and x.is_contiguous() and y.is_contiguous()
+    _call("generic", "nncpu_stream_axpy", _ptr(x), _ptr(y), _f(alpha), _l(x.numel()), _stream())
+
+
+def branch_norm_add(x, a, wa, b, wb, eps: float, alpha: float) -> None:
+    """x += alpha * (rmsnorm(a) * wa + rmsnorm(b) * wb) row by row (``b`` None: the first term alone; a weight None:
+    ones); x, a, b float32."""
+    n, dim = x.shape
+    assert x.dtype == a.dtype == torch.float32 and a.shape == x.shape and x.is_contiguous() and a.is_contiguous()
+    assert b is None or (b.dtype == torch.float32 and b.shape == x.shape and b.is_contiguous())
+    assert wa is None or wa.numel() == dim
+    assert wb is None or (wb.numel() == dim and (wa is None or wa.dtype == wb.dtype))
+    w = wa if wa is not None else wb
+    _call("generic", "nncpu_branch_norm_add", _ptr(x), _ptr(a), _ptr(wa), _ptr(b), _ptr(wb), _i(_code(w)), _f(eps),
+          _f(alpha), _i(n), _i(dim), _stream())
+
+
+def relu2(x, out) -> None:
+    """out = max(x, 0)^2; x float32."""
+    assert x.dtype == torch.float32 and x.shape == out.shape and x.is_contiguous() and out.is_contiguous()
+    _call("generic", "nncpu_unary_act", _ptr(x), _ptr(out), _i(_code(out)), _l(x.numel()), _i(0), _stream())
+
+
+def token_gate(z, table, ids, col: int, out) -> None:
+    """out[t, j] = gelu_tanh(z[t, j]) * table[ids[t], col + j]: lanes of a per-token table gate a projection; z float32."""
+    n, dim = z.shape
+    assert z.dtype == torch.float32 and z.is_contiguous() and out.shape == z.shape and out.is_contiguous()
+    assert table.dim() == 2 and table.is_contiguous() and 0 <= col and col + dim <= table.shape[1]
+    assert ids.dtype == torch.int32 and ids.numel() >= n
+    _call("generic", "nncpu_token_gate", _ptr(z), _ptr(table), _i(_code(table)), _ptr(ids), _i(table.shape[1]), _i(col),
+          _ptr(out), _i(_code(out)), _i(n), _i(dim), _stream())
+
+
 def rmsnorm_pair_supported(dim: int) -> bool:
     return dim > 0 and dim % 4 == 0 and dim <= 8192
 
@@ -195,12 +265,13 @@ PLANS = {"auto": 0, "even_from_17": 1, "never_even": 2, "no_pairs": 4, "narrow_u
 EPILOGUES = {"plain": 0, "swiglu": 1}
 
 
-_ACTIVATIONS = {"xielu": 1, "gelu_tanh": 2, "swish_clamp": 3}
+_ACTIVATIONS = {"xielu": 1, "gelu_tanh": 2, "swish_clamp": 3, "relu2": 4}
 
 
 def _activation(activation):
     """``activation`` None, or (kind, a, b).  With the plain epilogue ("xielu", a, b), a = softplus(p) and
-    b = 1/2 + softplus(q) ready-made: applied to the product's result after the bias (no accumulation).  With the
+    b = 1/2 + softplus(q) ready-made, or ("relu2", 0, 0), the square of relu: applied to the product's result after
+    the bias (no accumulation).  With the
     gated epilogue the gate's activation in place of SiLU: ("gelu_tanh", 0, 0) or ("swish_clamp", limit, 0), see
     ``gated_act``."""
     if activation is None:
@@ -654,28 +725,43 @@ def sigmoid_gate(x, gate, col: int) -> None:
           _stream())
 
 
-def moe_route(logits, top: int, ids, weights) -> None:
+def _route_mode(scoring):
+    """``scoring`` None: the softmax over the chosen logits alone.  ("all", n_groups, keep, scale): scores are the
+    softmax over all experts; the experts form ``n_groups`` equal groups of neighbours whose score is their best
+    expert's, and only experts of the ``keep`` best groups can be chosen (``n_groups`` <= 1: no groups); the weights
+    are the chosen scores divided by their sum (+ 1e-20), times ``scale``."""
+    if scoring is None:
+        return _i(0), _i(1), _i(1), _f(1.0)
+    kind, n_groups, keep, scale = scoring
+    if kind != "all":
+        raise InvalidArgument(f"a router cannot score by {kind!r}")
+    return _i(1), _i(max(1, n_groups)), _i(max(1, keep)), _f(scale)
+
+
+def moe_route(logits, top: int, ids, weights, scoring=None) -> None:
     """Per row of float32 logits [n, E]: ids [n, top] (int32) of the largest logits in descending order (the lower
-    index wins a tie) and weights [n, top] (float32), the softmax over those logits alone."""
+    index wins a tie) and weights [n, top] (float32), the softmax over those logits alone, or what ``scoring`` says
+    (see ``_route_mode``)."""
     n, E = logits.shape
     assert logits.dtype == torch.float32 and ids.dtype == torch.int32 and weights.dtype == torch.float32
     assert ids.shape == weights.shape == (n, top)
-    _call("generic", "nncpu_moe_route", _ptr(logits), _i(n), _i(E), _i(top), _ptr(ids), _ptr(weights), _stream())
+    _call("generic", "nncpu_moe_route", _ptr(logits), _i(n), _i(E), _i(top), _ptr(ids), _ptr(weights),
+          *_route_mode(scoring), _stream())
 
 
 def moe_router_fits(n_experts: int, width: int) -> bool:
     """Whether ``moe_router`` takes these sizes (a token's input and logits in one block's shared memory)."""
-    return 0 < n_experts <= 1024 and (width + n_experts) * 4 <= 48 * 1024
+    return 0 < n_experts <= 1024 and (width + 2 * n_experts) * 4 <= 48 * 1024
 
 
-def moe_router(x, w, bias, top: int, ids, weights) -> None:
+def moe_router(x, w, bias, top: int, ids, weights, scoring=None) -> None:
     """The router in one launch: logits = x . w^T + bias in 32-bit, then ``moe_route``'s choice and weights."""
     n, width = x.shape
     E = w.shape[0]
     assert w.shape == (E, width) and (bias is None or bias.numel() == E) and ids.shape == weights.shape == (n, top)
     assert ids.dtype == torch.int32 and weights.dtype == torch.float32
     _call("generic", "nncpu_moe_router", _ptr(x), _i(_code(x)), _ptr(w), _i(_code(w)), _ptr(bias), _i(_code(bias)), _i(n),
-          _i(E), _i(top), _i(width), _ptr(ids), _ptr(weights), _stream())
+          _i(E), _i(top), _i(width), _ptr(ids), _ptr(weights), *_route_mode(scoring), _stream())
 
 
 def moe_experts(x, w_gate, w_up, w_down, ids, weights, act, out, kind: str, limit: float = 0.0) -> None:
@@ -769,18 +855,22 @@ def gla_decay(z, tau: float) -> None:
 
 
 def gla_step(proj, z, state, seq_slots, weight, eps: float, out, n_heads: int, d: int, e: int, q_scale: float,
-             tau: float) -> None:
+             tau: float, head_decay=None) -> None:
     """A decode step of gated linear attention, one token per sequence: the recurrence on ``state`` (as ``gla_scan``
     with sequences of one token, ``z`` holding logits), then the heads' norm, weight and gate (as ``gla_output``),
-    in one launch.  ``out`` [n, H e] in float32 or bfloat16."""
+    in one launch.  ``out`` [n, H e] in float32 or bfloat16.  ``head_decay`` (float32 [H]): one fixed decay per head
+    in place of the decays from ``z`` (which may then be None); ``weight`` None: ones."""
     n = out.shape[0]
-    assert proj.dtype == z.dtype == state.dtype == torch.float32
-    assert proj.shape == (n, 2 * n_heads * (d + e)) and z.shape == (n, n_heads * d) and out.shape == (n, n_heads * e)
-    assert state.shape[1:] == (n_heads, d, e) and state.is_contiguous() and proj.is_contiguous() and weight.numel() == e
+    assert proj.dtype == state.dtype == torch.float32 and (z is None or z.dtype == torch.float32)
+    assert proj.shape == (n, 2 * n_heads * (d + e)) and out.shape == (n, n_heads * e)
+    assert (z is not None and z.shape == (n, n_heads * d)) or (head_decay is not None and head_decay.dtype == torch.float32
+                                                               and head_decay.numel() == n_heads)
+    assert state.shape[1:] == (n_heads, d, e) and state.is_contiguous() and proj.is_contiguous()
+    assert weight is None or weight.numel() == e
     assert seq_slots.dtype == torch.int32 and seq_slots.numel() >= n
     _call("recurrent", "nncpu_gla_step", _ptr(proj), _i(proj.shape[1]), _ptr(z), _ptr(state), _ptr(seq_slots),
           _ptr(weight), _i(_code(weight)), _f(eps), _ptr(out), _i(_code(out)), _i(n), _i(n_heads), _i(d), _i(e),
-          _f(q_scale), _f(tau), _stream())
+          _f(q_scale), _f(tau), _ptr(head_decay), _stream())
 
 
 def gla_scan_force_columns(cpl: int) -> None:
@@ -790,34 +880,56 @@ def gla_scan_force_columns(cpl: int) -> None:
 
 
 def gla_scan(proj, z, state, seq_slots, cu_seqlens, o, n_seqs: int, n_heads: int, d: int, e: int, q_scale: float,
-             tau: float, decays_given: bool = False) -> None:
+             tau: float, decays_given: bool = False, head_decay=None) -> None:
     """Gated linear attention's recurrence over the step's tokens, sequence by sequence in order.  ``proj``
     float32 [n, 2 H d + 2 H e] holds q, k, v and the output gate per token, ``z`` float32 [n, H d] the decay
     logits (with ``decays_given`` the decays themselves, as ``gla_decay`` leaves them); ``state`` float32 [slots, H, d, e] is read and left updated for the slots in ``seq_slots`` (a negative
-    slot: a padding sequence, zeros out); ``o`` float32 [n, H e] receives S_t^T q_t."""
+    slot: a padding sequence, zeros out); ``o`` float32 [n, H e] receives S_t^T q_t.  ``head_decay`` (float32 [H]):
+    one fixed decay per head for every key channel and token; ``z`` is then not read and may be None."""
     n = o.shape[0]
-    assert proj.dtype == z.dtype == state.dtype == o.dtype == torch.float32
-    assert proj.shape == (n, 2 * n_heads * (d + e)) and z.shape == (n, n_heads * d) and o.shape == (n, n_heads * e)
+    assert proj.dtype == state.dtype == o.dtype == torch.float32 and (z is None or z.dtype == torch.float32)
+    assert proj.shape == (n, 2 * n_heads * (d + e)) and o.shape == (n, n_heads * e)
+    assert (z is not None and z.shape == (n, n_heads * d)) or (head_decay is not None and head_decay.dtype == torch.float32
+                                                               and head_decay.numel() == n_heads)
     assert state.shape[1:] == (n_heads, d, e) and state.is_contiguous() and proj.is_contiguous()
     assert seq_slots.dtype == torch.int32 and cu_seqlens.dtype == torch.int32 and cu_seqlens.numel() >= n_seqs + 1
     _call("recurrent", "nncpu_gla_scan", _ptr(proj), _i(proj.shape[1]), _ptr(z), _ptr(state), _ptr(seq_slots),
           _ptr(cu_seqlens), _ptr(o), _i(n_seqs), _i(n_heads), _i(d), _i(e), _f(q_scale), _f(tau), _i(decays_given),
-          _stream())
+          _ptr(head_decay), _stream())
 
 
-def gla_output(o, proj, weight, eps: float, out, n_heads: int, d: int, e: int, gate_col: int = -1) -> None:
+OUTPUT_GATES = {"silu": 0, "sigmoid": 1}
+
+
+def gla_output(o, proj, weight, eps: float, out, n_heads: int, d: int, e: int, gate_col: int = -1,
+               gate: str = "silu") -> None:
     """out[t, h] = o[t, h] / rms(o[t, h]) * weight * silu(g[t, h]) with g the H e lanes of ``proj``'s rows from column
-    ``gate_col`` (default: after 2 H d + H e lanes, where gated linear attention keeps them)."""
+    ``gate_col`` (default: after 2 H d + H e lanes, where gated linear attention keeps them).  ``weight`` None: ones;
+    ``gate`` "sigmoid": sigmoid(g) in place of silu(g)."""
     n = o.shape[0]
     assert o.dtype == proj.dtype == torch.float32 and o.shape == (n, n_heads * e) and out.shape == o.shape
-    assert weight.numel() == e
+    assert weight is None or weight.numel() == e
     _call("recurrent", "nncpu_gla_output", _ptr(o), _ptr(proj), _i(proj.shape[1]),
           _i(gate_col if gate_col >= 0 else 2 * n_heads * d + n_heads * e),
-          _ptr(weight), _i(_code(weight)), _f(eps), _ptr(out), _i(_code(out)), _i(n), _i(n_heads), _i(e), _stream())
+          _ptr(weight), _i(_code(weight)), _f(eps), _ptr(out), _i(_code(out)), _i(n), _i(n_heads), _i(e),
+          _i(OUTPUT_GATES[gate]), _stream())
+
+
+def retention_prepare(proj, cos_sin, n_heads: int, d: int, k_scale: float) -> None:
+    """In place on ``proj`` float32 [n, >= 2 H d], whose rows begin with q (H d) and k (H d): both are rotated by the
+    token's position (``cos_sin`` float32 [n, half, 2]: the pairs (i, i + half) of a head's first 2 half lanes; None:
+    no rotation), then k is multiplied by ``k_scale``.  What retention's recurrence reads."""
+    n = proj.shape[0]
+    half = 0 if cos_sin is None else cos_sin.shape[1]
+    assert proj.dtype == torch.float32 and proj.is_contiguous() and proj.shape[1] >= 2 * n_heads * d
+    assert cos_sin is None or (cos_sin.dtype == torch.float32 and cos_sin.shape == (n, half, 2) and cos_sin.is_contiguous())
+    _call("recurrent", "nncpu_retention_prepare", _ptr(proj), _i(proj.shape[1]), _ptr(cos_sin), _i(half), _i(n),
+          _i(n_heads), _i(d), _f(k_scale), _stream())
 
 
 def delta_prepare(proj, conv_w, state, conv_col: int, tok_seq, seq_slots, cu_seqlens, a_log, dt_bias, xc, gb, n_seqs: int,
-                  n_heads: int, n_kv: int, d: int, e: int, taps: int, one_token_each: bool = False) -> None:
+                  n_heads: int, n_kv: int, d: int, e: int, taps: int, one_token_each: bool = False, beta_col: int = -1,
+                  chan_z=None) -> None:
     """What the gated delta rule's recurrence reads, from the projections: ``proj`` float32 [n, >= C + H e + 2 H] holds
     per token q (G d), k (G d), v (H e) (the C channels of the short convolutions), the output gate's logits (H e), the
     logits of beta (H) and the decays' inputs (H).  ``xc`` float32 [n, C] receives silu(conv(.)) with q and k made unit
@@ -825,20 +937,27 @@ def delta_prepare(proj, conv_w, state, conv_col: int, tok_seq, seq_slots, cu_seq
     and then beta = sigmoid(b).  ``conv_w`` [C, taps]; ``state`` float32 [slots, L] holds from lane ``conv_col`` of a
     slot's row [taps - 1, C]: the sequence's last inputs; it is left advanced by the step's tokens.
     ``one_token_each``: every sequence of the step brings exactly one token (the kept inputs then advance inside the one
-    kernel; otherwise a second kernel advances them after all tokens have read them)."""
+    kernel; otherwise a second kernel advances them after all tokens have read them).
+    ``beta_col``: the column of ``proj`` where beta's logits start (default C + H e; the decays' inputs follow them).
+    ``chan_z`` float32 [n, H d]: a decay per head and key channel; it holds softplus's argument (bias included) and
+    receives exp(-exp(A_log_h) softplus(.)) in place; ``proj`` then has no decay inputs, ``dt_bias`` is not read and
+    ``gb``'s decays are ones."""
     n = xc.shape[0]
     C = 2 * n_kv * d + n_heads * e
+    if beta_col < 0:
+        beta_col = C + n_heads * e
     assert proj.dtype == xc.dtype == gb.dtype == state.dtype == torch.float32 and proj.is_contiguous()
-    assert proj.shape[0] == n and proj.shape[1] >= C + n_heads * e + 2 * n_heads and xc.shape == (n, C)
+    assert proj.shape[0] == n and proj.shape[1] >= beta_col + (1 if chan_z is not None else 2) * n_heads and xc.shape == (n, C)
+    assert chan_z is None or (chan_z.dtype == torch.float32 and chan_z.shape == (n, n_heads * d) and chan_z.is_contiguous())
     assert gb.shape == (n, 2 * n_heads) and conv_w.shape == (C, taps) and conv_w.is_contiguous()
     assert state.dim() == 2 and state.shape[1] >= conv_col + (taps - 1) * C and state.is_contiguous()
-    assert a_log.numel() == dt_bias.numel() == n_heads and a_log.dtype == dt_bias.dtype
+    assert a_log.numel() == n_heads and (chan_z is not None or (dt_bias.numel() == n_heads and a_log.dtype == dt_bias.dtype))
     assert tok_seq.dtype == seq_slots.dtype == cu_seqlens.dtype == torch.int32 and cu_seqlens.numel() >= n_seqs + 1
     _call("recurrent", "nncpu_delta_prepare", _ptr(proj), _i(proj.shape[1]), _ptr(conv_w), _i(_code(conv_w)),
           None if (state.is_meta and _dry) else _vp(state.data_ptr() + 4 * conv_col), _l(state.shape[1]), _ptr(tok_seq), _ptr(seq_slots), _ptr(cu_seqlens), _ptr(a_log),
           _ptr(dt_bias), _i(_code(a_log)),
           _ptr(xc), _ptr(gb), _i(n), _i(n_seqs), _i(n_heads), _i(n_kv), _i(d), _i(e), _i(taps), _f(d ** -0.5),
-          _i(one_token_each), _stream())
+          _i(one_token_each), _i(beta_col), _ptr(chan_z), _stream())
 
 
 def delta_scan_force(lanes: int = 0, columns: int = 0) -> None:
@@ -850,19 +969,22 @@ def delta_scan_force(lanes: int = 0, columns: int = 0) -> None:
     lib.nncpu_delta_scan_force_columns(ctypes.c_int(int(columns)))
 
 
-def delta_scan(xc, gb, state, seq_slots, cu_seqlens, o, n_seqs: int, n_heads: int, n_kv: int, d: int, e: int) -> None:
+def delta_scan(xc, gb, state, seq_slots, cu_seqlens, o, n_seqs: int, n_heads: int, n_kv: int, d: int, e: int,
+               chan_g=None) -> None:
     """The gated delta rule over the step's tokens, sequence by sequence in order: per head S <- g S;
     u = beta (v - S^T k); S <- S + k u^T; o = S^T q, with q, k, v from ``xc`` and g, beta from ``gb`` as
     ``delta_prepare`` leaves them.  ``state`` float32 [slots, >= H d e] (a slot's [H, d, e] in the first lanes of its
     row) is read and left updated for the slots in
-    ``seq_slots`` (negative: a padding sequence, zeros out); ``o`` float32 [n, H e]."""
+    ``seq_slots`` (negative: a padding sequence, zeros out); ``o`` float32 [n, H e].  ``chan_g`` float32 [n, H d]: a
+    decay per head and key channel, S <- diag(g) S, in place of ``gb``'s one per head."""
     n = o.shape[0]
+    assert chan_g is None or (chan_g.dtype == torch.float32 and chan_g.shape == (n, n_heads * d) and chan_g.is_contiguous())
     assert xc.dtype == gb.dtype == state.dtype == o.dtype == torch.float32
     assert xc.shape == (n, 2 * n_kv * d + n_heads * e) and gb.shape == (n, 2 * n_heads) and o.shape == (n, n_heads * e)
     assert state.dim() == 2 and state.shape[1] >= n_heads * d * e and state.is_contiguous()
     assert xc.is_contiguous() and gb.is_contiguous()
     assert seq_slots.dtype == torch.int32 and cu_seqlens.dtype == torch.int32 and cu_seqlens.numel() >= n_seqs + 1
-    _call("recurrent", "nncpu_delta_scan", _ptr(xc), _ptr(gb), _ptr(state), _l(state.shape[1]), _ptr(seq_slots), _ptr(cu_seqlens), _ptr(o),
+    _call("recurrent", "nncpu_delta_scan", _ptr(xc), _ptr(gb), _ptr(chan_g), _ptr(state), _l(state.shape[1]), _ptr(seq_slots), _ptr(cu_seqlens), _ptr(o),
           _i(n_seqs), _i(n_heads), _i(n_kv), _i(d), _i(e), _stream())
 
 

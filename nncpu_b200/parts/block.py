@@ -13,17 +13,27 @@ from ..kernels import ops
 from ..weights.params import ParamSpec
 from . import base
 from .base import Block, NormRequest, register_block
+from .side import TokenSide
 
 
 @register_block("prenorm")
 class PreNormBlock(Block):
+    """x += m * mixer(norm1(x)); x += m * feed_forward(norm2(x)); then, if the layer has one, its per-layer token input
+    (``parts.side``).  m = ``residual_mult``.  With m = 1 the sublayers add into the stream themselves.  With another m
+    a sublayer that says ``scales_output`` is told the factor (``ctx.out_scale``) and still adds into the stream; any
+    other writes into a 32-bit branch of its own (told that it is fresh, so its last product writes instead of adding)
+    which one kernel adds to the stream times m.  A layer may go without a feed-forward (its second norm is then not
+    used, and its tensors are not asked for)."""
+
     def __init__(self, spec, reads_other_cache: bool = False):
         self.norm1 = base.build("norm", spec.norm1)
         kwargs = {"reads_other_cache": True} if reads_other_cache else {}
         self.mixer = base.build("mixer", spec.mixer, **kwargs)
-        self.norm2 = base.build("norm", spec.norm2)
-        self.feed_forward = base.build("feed_forward", spec.feed_forward)
-        self._parts = (self.norm1, self.mixer, self.norm2, self.feed_forward)
+        self.feed_forward = None if spec.feed_forward is None else base.build("feed_forward", spec.feed_forward)
+        self.norm2 = None if self.feed_forward is None else base.build("norm", spec.norm2)
+        self.mult = float(spec.residual_mult)
+        self.side = None if spec.side is None else TokenSide(spec.side)
+        self._parts = tuple(p for p in (self.norm1, self.mixer, self.norm2, self.feed_forward, self.side) if p is not None)
 
     def params(self):
         return [p for part in self._parts for p in part.params()]
@@ -51,22 +61,61 @@ class PreNormBlock(Block):
             return request.result
         return norm.forward(ctx, residual)
 
+    def _scaled(self, ctx, part, residual, run):
+        """x += m * part(...) for m != 1: ``run(out)`` makes the part add into (or, for a fresh branch, write) ``out``."""
+        if getattr(part, "scales_output", False):
+            ctx.out_scale = self.mult
+            try:
+                run(residual)
+            finally:
+                ctx.out_scale = 1.0
+            return
+        branch = self.rt.empty(*residual.shape, dtype=torch.float32)
+        ctx.branch_is_fresh = True
+        try:
+            run(branch)
+        finally:
+            ctx.branch_is_fresh = False
+        with self.rt.phase("norm", nbytes=12.0 * residual.numel()):
+            ops.stream_axpy(residual, branch, self.mult)
+
     def forward(self, ctx, residual, caches):
         # At a few tokens the norms ride on the products around them: the block before may have left norm1's
         # input (ctx.next_norm), the mixer's last product is asked for norm2's, and the feed-forward's last
         # product for the first norm of the block that follows (ctx.after_block).
         handed, after = ctx.next_norm, ctx.after_block
         ctx.next_norm = ctx.after_block = None
+        ff = self.feed_forward
+        if self.mult != 1.0 or self.side is not None:
+            # the sublayers' products are not the last writes into the stream: no norm rides on them
+            with self.rt.scope():
+                x = self.norm1.forward(ctx, residual)
+                if self.mult != 1.0:
+                    self._scaled(ctx, self.mixer, residual, lambda out: self.mixer.forward(ctx, x, out, caches[0]))
+                else:
+                    self.mixer.forward(ctx, x, residual, caches[0])
+            if ff is not None:
+                with self.rt.scope():
+                    x = self.norm2.forward(ctx, residual)
+                    if self.mult != 1.0:
+                        self._scaled(ctx, ff, residual, lambda out: ff.forward(ctx, x, out))
+                    else:
+                        ff.forward(ctx, x, residual)
+            if self.side is not None:
+                self.side.forward(ctx, residual, self.mult)
+            return
         with self.rt.scope():       # the mixer's temporaries are done with when the feed-forward starts
             x = self._normed(self.norm1, self.mixer, ctx, residual, handed)
-            asked = self.norm2.request(ctx, residual) if self.feed_forward.accepts_deferred_norm else None
-            ctx.next_norm = asked
+            asked = self.norm2.request(ctx, residual) if (ff is not None and ff.accepts_deferred_norm) else None
+            ctx.next_norm = asked if ff is not None else after
             self.mixer.forward(ctx, x, residual, caches[0])
-            ctx.next_norm = None
-        with self.rt.scope():
-            x = self._normed(self.norm2, self.feed_forward, ctx, residual, asked)
-            ctx.next_norm = after
-            self.feed_forward.forward(ctx, x, residual)
+            if ff is not None:
+                ctx.next_norm = None
+        if ff is not None:
+            with self.rt.scope():
+                x = self._normed(self.norm2, ff, ctx, residual, asked)
+                ctx.next_norm = after
+                ff.forward(ctx, x, residual)
         # ctx.next_norm stays: the block that follows finds its request there, fulfilled or not
 
 

@@ -96,13 +96,27 @@ class RoutedExperts(FeedForward):
 
     The router is a 32-bit product (its input may be the run's rounding of the norm's output) with a bias; the choice
     and the weights are made on the device by one kernel, so a step never waits for the host.  Experts' matrices are
-    stacked [n_experts, rows, cols] when the weights are bound."""
+    stacked [n_experts, rows, cols] when the weights are bound.
+
+    ``scores`` "all" (see ``RoutedExpertsSpec``): the softmax runs over all experts, the choice may be limited to the
+    best groups of experts, and the chosen scores are divided by their sum and multiplied by ``weight_scale``.
+    ``out_scale`` (and the step's ``ctx.out_scale``) multiply what the part adds to the stream: they enter the
+    tokens' weights, so the sum over a token's experts is scaled at no cost."""
+    scales_output = True
 
     def __init__(self, spec):
         if spec.activation not in GATED_ACTIVATIONS:
             raise UnsupportedModel(f"{spec.name}: activation {spec.activation!r} is not supported")
         if not 0 < spec.top <= spec.n_experts:
             raise UnsupportedModel(f"{spec.name}: the top {spec.top} of {spec.n_experts} experts")
+        if spec.scores not in ("chosen", "all"):
+            raise UnsupportedModel(f"{spec.name}: router scores of kind {spec.scores!r}")
+        if spec.scores == "chosen" and (spec.n_groups > 1 or spec.weight_scale != 1.0 or spec.out_scale != 1.0):
+            raise UnsupportedModel(f"{spec.name}: groups and scales go with scores over all experts")
+        if spec.n_groups > 1 and (spec.n_experts % spec.n_groups or not 1 <= spec.keep_groups <= spec.n_groups
+                                  or spec.keep_groups * (spec.n_experts // spec.n_groups) < spec.top):
+            raise UnsupportedModel(f"{spec.name}: the {spec.keep_groups} best of {spec.n_groups} groups of "
+                                   f"{spec.n_experts} experts cannot give the top {spec.top}")
         self.spec = spec
         self.shared = None if spec.shared is None else GatedMlp(spec.shared)
 
@@ -112,8 +126,9 @@ class RoutedExperts(FeedForward):
             p += [ParamSpec(f"{s.name}.e{e}.gate", (s.intermediate_size, s.hidden_size)),
                   ParamSpec(f"{s.name}.e{e}.up", (s.intermediate_size, s.hidden_size)),
                   ParamSpec(f"{s.name}.e{e}.down", (s.hidden_size, s.intermediate_size))]
-        p += [ParamSpec(f"{s.name}.router", (s.n_experts, s.hidden_size), init=("normal", 0.5)),
-              ParamSpec(f"{s.name}.router.b", (s.n_experts,), init=("normal", 0.5))]
+        p.append(ParamSpec(f"{s.name}.router", (s.n_experts, s.hidden_size), init=("normal", 0.5)))
+        if s.router_bias:
+            p.append(ParamSpec(f"{s.name}.router.b", (s.n_experts,), init=("normal", 0.5)))
         return p + (self.shared.params() if self.shared is not None else [])
 
     def bind(self, tensors, rt):
@@ -134,7 +149,7 @@ class RoutedExperts(FeedForward):
         else:
             self.w_gate, self.w_up = gate, up
         del gate, up
-        self.w_router, self.b_router = tensors[f"{s.name}.router"], tensors[f"{s.name}.router.b"]
+        self.w_router, self.b_router = tensors[f"{s.name}.router"], tensors.get(f"{s.name}.router.b")
         if self.shared is not None:
             self.shared.bind(tensors, rt)
 
@@ -154,10 +169,16 @@ class RoutedExperts(FeedForward):
             raise UnsupportedModel(f"{s.name}: routed experts add into the stream they are given")
         ids = rt.empty(n, s.top, dtype=torch.int32)
         weights = rt.empty(n, s.top, dtype=torch.float32)
+        out_scale = float(getattr(ctx, "out_scale", 1.0)) * s.out_scale
+        scoring = None
+        if s.scores == "all":
+            scoring = ("all", s.n_groups, s.keep_groups, s.weight_scale * out_scale)
+        elif out_scale != 1.0:
+            raise UnsupportedModel(f"{s.name}: a scaled output goes with scores over all experts")
         with rt.phase("moe_route", self.w_router, n):
             many = n >= ROUTER_PRODUCT_FROM_TOKENS and rt.tensor_cores_take(x.dtype, self.w_router, s.hidden_size)
             if not many and ops.moe_router_fits(s.n_experts, s.hidden_size):
-                ops.moe_router(x, self.w_router, self.b_router, s.top, ids, weights)
+                ops.moe_router(x, self.w_router, self.b_router, s.top, ids, weights, scoring)
             else:
                 # many tokens: the logits as a product of their own (bfloat16 operands are multiplied exactly and
                 # added in 32-bit on the tensor cores; a float32 run, and sizes those refuse, use the CUDA cores)
@@ -166,7 +187,7 @@ class RoutedExperts(FeedForward):
                     rt.linear(x, self.w_router, self.b_router, logits)
                 else:
                     ops.linear_simt(x, self.w_router, self.b_router, logits)
-                ops.moe_route(logits, s.top, ids, weights)
+                ops.moe_route(logits, s.top, ids, weights, scoring)
         S, f, h = n * s.top, s.intermediate_size, s.hidden_size
         esize = self.w_gate.element_size()
         experts_read = min(S, s.n_experts)
@@ -193,37 +214,43 @@ class RoutedExperts(FeedForward):
             with rt.phase("moe_experts", nbytes=experts_read * 3.0 * f * h * esize, flops=6.0 * S * f * h):
                 ops.moe_experts(x, self.w_gate, self.w_up, self.w_down, ids, weights, mid, residual, s.activation, s.limit)
         if self.shared is not None:
+            if out_scale != 1.0:
+                raise UnsupportedModel(f"{s.name}: a shared expert under a scaled output")
             self.shared.forward(ctx, x, residual)
 
 
 @register_feed_forward("dense_mlp")
 class DenseMlp(FeedForward):
-    """down(xielu(up(x) + b_up)) + b_down.  The activation (softplus of its two numbers included) is computed in
+    """down(act(up(x) + b_up)) + b_down with act xIELU or the square of relu; ``bias`` False: no biases.  The activation (softplus of xIELU's two numbers included) is computed in
     32-bit on the up product's 32-bit result, in the product's epilogue where it runs on the tensor cores and in a
     kernel of its own elsewhere; its output is rounded to the run's element type for the down product.  Tensors: ``<name>.up``, ``.up.b``, ``.down``, ``.down.b``, ``.act`` (p, q)."""
 
     def __init__(self, spec):
-        if spec.activation != "xielu":
-            raise UnsupportedModel(f"{spec.name}: activation {spec.activation!r} is not supported (supported: xielu)")
+        if spec.activation not in ("xielu", "relu2"):
+            raise UnsupportedModel(f"{spec.name}: activation {spec.activation!r} is not supported (supported: xielu, relu2)")
         self.spec = spec
 
     def params(self):
         s = self.spec
-        return [ParamSpec(f"{s.name}.up", (s.intermediate_size, s.hidden_size)),
-                ParamSpec(f"{s.name}.up.b", (s.intermediate_size,)),
-                ParamSpec(f"{s.name}.down", (s.hidden_size, s.intermediate_size)),
-                ParamSpec(f"{s.name}.down.b", (s.hidden_size,)),
-                ParamSpec(f"{s.name}.act", (2,), init=("normal", 0.5))]
+        p = [ParamSpec(f"{s.name}.up", (s.intermediate_size, s.hidden_size)),
+             ParamSpec(f"{s.name}.down", (s.hidden_size, s.intermediate_size))]
+        if s.bias:
+            p += [ParamSpec(f"{s.name}.up.b", (s.intermediate_size,)), ParamSpec(f"{s.name}.down.b", (s.hidden_size,))]
+        if s.activation == "xielu":
+            p.append(ParamSpec(f"{s.name}.act", (2,), init=("normal", 0.5)))
+        return p
 
     def bind(self, tensors, rt):
         s, self.rt = self.spec, rt
-        self.w_up, self.b_up = tensors[f"{s.name}.up"], tensors[f"{s.name}.up.b"]
-        self.w_down, self.b_down = tensors[f"{s.name}.down"], tensors[f"{s.name}.down.b"]
-        self.act = tensors[f"{s.name}.act"]
-        # On the tensor-core path the activation runs in the up product's epilogue, on its 32-bit accumulators; its
+        self.w_up, self.b_up = tensors[f"{s.name}.up"], tensors.get(f"{s.name}.up.b")
+        self.w_down, self.b_down = tensors[f"{s.name}.down"], tensors.get(f"{s.name}.down.b")
+        self.act = tensors.get(f"{s.name}.act")
+        # On the tensor-core path the activation runs in the up product's epilogue, on its 32-bit accumulators; xIELU's
         # two numbers enter as softplus(p) and 1/2 + softplus(q), worked out once here in 32-bit.
-        self.fused = rt.tensor_cores_take(rt.dtype, self.w_up, s.hidden_size) and not self.act.is_meta
-        if self.fused:
+        self.fused = rt.tensor_cores_take(rt.dtype, self.w_up, s.hidden_size) and (self.act is None or not self.act.is_meta)
+        if self.fused and s.activation == "relu2":
+            self.activation = ("relu2", 0.0, 0.0)
+        elif self.fused:
             p, q = (math.log1p(math.exp(-abs(v))) + max(v, 0.0) for v in self.act.detach().float().tolist())   # softplus
             self.activation = ("xielu", p, 0.5 + q)
 
@@ -242,6 +269,9 @@ class DenseMlp(FeedForward):
             with rt.phase("ffn_up", self.w_up, n):
                 rt.linear(x, self.w_up, self.b_up, up)
             with rt.phase("ffn_act"):
-                ops.xielu(up, self.act, act)
+                if s.activation == "relu2":
+                    ops.relu2(up, act)
+                else:
+                    ops.xielu(up, self.act, act)
         with rt.phase("ffn_down", self.w_down, n):
             rt.linear(act, self.w_down, self.b_down, residual, accumulate=not getattr(ctx, "branch_is_fresh", False))

@@ -1,4 +1,4 @@
-"""RMSNorm with learned weights: y = x / sqrt(mean(x^2) + eps) * (gamma + offset)
+"""Norms.  RMSNorm with learned weights: y = x / sqrt(mean(x^2) + eps) * (gamma + offset)
 (crates/nncpu/src/kernels/scalar.rs:270-292), computed in 32-bit.  ``offset`` is 0 for weights stored around
 one and 1 for weights stored around zero."""
 from __future__ import annotations
@@ -45,3 +45,30 @@ class RMSNorm(Norm):
                 or not self.rt.fuses_norms(ctx.n_tokens, self.size)):
             return None
         return NormRequest(self, residual, self.gamma, self.eps, self.size)
+
+
+@register_norm("layernorm")
+class LayerNorm(Norm):
+    """y = (x - mean) / sqrt(var + eps) * w + b over the row, var the mean of the squared deviations from the mean;
+    32-bit.  It does not ride on the products around it (they carry sums of squares, not means)."""
+
+    def __init__(self, spec):
+        self.size, self.eps, self.name = spec.size, spec.eps, spec.name
+        self.tensor = spec.name + spec.suffix
+        self.bias_tensor = self.tensor + spec.bias_suffix
+        self.gamma = self.beta = None
+
+    def params(self):
+        return [ParamSpec(self.tensor, (self.size,), init=("one_plus_normal", 0.1)),
+                ParamSpec(self.bias_tensor, (self.size,), init=("normal", 0.1))]
+
+    def bind(self, tensors, rt):
+        self.rt = rt
+        self.gamma, self.beta = tensors[self.tensor], tensors[self.bias_tensor]
+
+    def forward(self, ctx, residual, rows=None):
+        n = residual.shape[0] if rows is None else rows.numel()
+        out = self.rt.empty(n, self.size)
+        with self.rt.phase("norm"):
+            ops.layernorm(residual, self.gamma, self.beta, self.eps, out, rows)
+        return out
