@@ -16,7 +16,8 @@ with host token ids in and out.  The line also carries a prefill measurement (on
 ``--workload NAME`` runs another measurement instead and prints its own JSON: ``14b-unequal``, ``32b`` and
 ``long-context`` (larger Qwen3 sizes end to end), ``romepel`` / ``zevivik`` (those designs at two widths beside Qwen3
 layers of equal size: a 2 048-token prompt, decode at batch 8, and every phase's time and roofline fraction), and
-``pikalorn`` (that design at two widths beside Zevivik and Romepel layers of equal size, measured the same way).
+``pikalorn`` (that design at two widths beside Zevivik and Romepel layers of equal size, measured the same way),
+``vodalorn`` (that design at two widths beside Pikalorn and Zevivik layers of equal size, measured the same way).
 """
 from __future__ import annotations
 
@@ -236,6 +237,7 @@ WORKLOADS = {
     "romepel": dict(model="8b"),
     "zevivik": dict(model="8b"),
     "pikalorn": dict(model="8b"),
+    "vodalorn": dict(model="8b"),
 }
 
 # `--workload romepel`: the Romepel design (recurrent gla layers, windowed attention with a distance bias, sandwich
@@ -370,6 +372,75 @@ def pikalorn_configs(z: dict):
     return pik, zev, rom
 
 
+# `--workload vodalorn`: the Vodalorn design (pre-norm layers with layer norms and a residual weight; pairs of windowed
+# softmax attention and retention; the gated delta rule with a decay per key channel; the square of relu; experts chosen
+# among the best groups; a hashed embedding of token pairs; a per-layer token input; a looped range of layers whose
+# passes start from a product with the embedding output) at sizes that resemble a real model's layers, beside the two
+# closest existing designs at equal width, layer runs, head counts and active feed-forward width: Pikalorn (attention
+# where Vodalorn has a pair, its delta rule at the same places, gated feed-forwards) and Zevivik (a loop over the same
+# range, routed experts of the same sizes at the same places, attention everywhere).
+VODALORN_SIZES = {
+    "2048": dict(width=2048, heads=16, kv_heads=4, dim=128, window=1024, ret_heads=8, ret_dim=128, inter=6144,
+                 delta_heads=16, delta_kv=8, delta_dim=128, delta_vdim=128, conv=4, rank=64, experts=16, top=2, groups=(4, 2),
+                 side=128, buckets=65521, vocab=32768),
+    "4096": dict(width=4096, heads=32, kv_heads=8, dim=128, window=1024, ret_heads=16, ret_dim=128, inter=12288,
+                 delta_heads=32, delta_kv=16, delta_dim=128, delta_vdim=128, conv=4, rank=128, experts=16, top=2, groups=(4, 2),
+                 side=256, buckets=65521, vocab=65536),
+}
+
+
+def vodalorn_configs(z: dict):
+    """(Vodalorn configuration, Pikalorn's and Zevivik's of equal size).  Five layers (pair + dense, delta + experts,
+    pair + experts, pair + experts, delta + dense) of which the three in the middle run twice: eight layer runs."""
+    from nncpu_b200.config import config_from_dict
+    rot = {"base": 1000000.0, "dims": z["dim"]}
+    # a token's active feed-forward width is the gated one's: experts of a quarter of it (three matrices each, the top
+    # 2), and a dense one with two matrices of 1.5 times it
+    moe = {"kind": "moe", "expert": {"ff": z["inter"] // 4, "limit": 7.0},
+           "router": {"experts": z["experts"], "top": z["top"], "scale": 1.0, "groups": {"count": z["groups"][0], "keep": z["groups"][1]}}}
+    dense = {"kind": "dense", "ff": z["inter"] * 3 // 2}
+
+    def pair(mlp):
+        return {"type": "parallel", "mlp": mlp,
+                "mixer": {"left": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
+                                   "scale": z["dim"] ** -0.5, "mask": {"size": z["window"]}, "rot": rot},
+                          "right": {"heads": z["ret_heads"], "dim": z["ret_dim"], "vdim": z["ret_dim"],
+                                    "decay": [1.0 - 2.0 ** -(5 + i % 8) for i in range(z["ret_heads"])],
+                                    "rot": {"base": 10000.0, "dims": z["ret_dim"]}}}}
+
+    def delta(mlp):
+        return {"type": "channel_delta", "mlp": mlp,
+                "mixer": {"heads": z["delta_heads"], "kv_heads": z["delta_kv"], "dim": z["delta_dim"], "vdim": z["delta_vdim"],
+                          "conv": z["conv"], "rank": z["rank"], "gate_rank": z["rank"]}}
+
+    vod = config_from_dict({"architecture": "Vodalorn", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+                            "residual_mult": 0.7, "token_side": {"dim": z["side"]},
+                            "embedding": {"bigram": {"buckets": z["buckets"], "mul_prev": 127, "mul_cur": 17}},
+                            "loop": {"start": 1, "stop": 4, "times": 2},
+                            "layers": [pair(dense), delta(moe), pair(moe), pair(moe), delta(dense)]})
+    gated = {"kind": "dense", "ff": z["inter"]}
+    patt = {"type": "attention", "mlp": gated,
+            "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
+                      "scale": z["dim"] ** -0.5, "rot": rot}}
+    pdel = {"type": "delta", "mlp": gated,
+            "mixer": {"heads": z["delta_heads"], "kv_heads": z["delta_kv"], "dim": z["delta_dim"], "vdim": z["delta_vdim"],
+                      "conv": z["conv"]}}
+    pik = config_from_dict({"architecture": "Pikalorn", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+                            "embedding": {"scale": 1.0},
+                            "layers": [patt, pdel, patt, patt, pdel, patt, patt, pdel]})
+    zmoe = {"kind": "moe", "expert": {"ff": z["inter"] // 4, "limit": 7.0}, "router": {"experts": z["experts"], "top": z["top"]}}
+
+    def zatt(mlp):
+        return {"type": "attention", "mlp": mlp,
+                "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
+                          "scale": z["dim"] ** -0.5, "mask": {"size": z["window"]}, "rot": rot}}
+
+    zev = config_from_dict({"architecture": "Zevivik", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+                            "embedding": {"scale": 1.0}, "loop": {"start": 1, "stop": 4, "times": 2},
+                            "layers": [zatt(gated), zatt(zmoe), zatt(zmoe), zatt(zmoe), zatt(gated)]})
+    return vod, pik, zev
+
+
 def phase_table(totals: dict, calls: int, pk: dict) -> dict:
     """Per phase of the profiler: milliseconds per step and, where the phase states its bytes and operations, the
     fraction of the roofline (the slower of bytes / copy bandwidth and operations / tensor throughput, over the time)."""
@@ -472,6 +543,18 @@ def run_pikalorn() -> dict:
         out["sizes"][name] = {"config": z, "pikalorn": run_design_point(pik, z["vocab"], pk),
                               "zevivik_same_size": run_design_point(zev, z["vocab"], pk),
                               "romepel_same_size": run_design_point(rom, z["vocab"], pk)}
+    return out
+
+
+def run_vodalorn() -> dict:
+    pk = peaks()
+    out = {"workload": "vodalorn", "dtype": "bf16", "peaks": pk["source"], "prompt": PROMPT,
+           "data": "synthetic: random weights, uniform random token ids", "sizes": {}}
+    for name, z in VODALORN_SIZES.items():
+        vod, pik, zev = vodalorn_configs(z)
+        out["sizes"][name] = {"config": z, "vodalorn": run_design_point(vod, z["vocab"], pk),
+                              "pikalorn_same_size": run_design_point(pik, z["vocab"], pk),
+                              "zevivik_same_size": run_design_point(zev, z["vocab"], pk)}
     return out
 
 
@@ -640,7 +723,7 @@ def main() -> int:
         return 0
     if args.workload:
         special = {"long-context": run_long_context, "romepel": run_romepel, "zevivik": run_zevivik,
-                   "pikalorn": run_pikalorn}
+                   "pikalorn": run_pikalorn, "vodalorn": run_vodalorn}
         print(json.dumps(special[args.workload]() if args.workload in special else run_workload(args.workload)))
         return 0
     model = Model.random(cfg, seed=0, dtype="bfloat16", device="cuda:0")

@@ -131,7 +131,7 @@ def parse_options(argv: List[str]) -> Options:
 
 
 def usage(argv0: str = "nncpu-b200") -> str:
-    return f"""nncpu-b200 {__version__} - run Qwen3, Romepel and Zevivik models on one B200
+    return f"""nncpu-b200 {__version__} - run Qwen3, Romepel, Zevivik, Pikalorn and Vodalorn models on one B200
 
 usage: {argv0} -m DIR --tokens "ID ID ..."   continue the token ids and exit
        {argv0} -m DIR -p TEXT                answer one message and exit (needs tokenizer.json in DIR)

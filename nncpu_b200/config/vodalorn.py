@@ -389,7 +389,7 @@ class VodalornConfig:
                 side = TokenSideSpec(name=f"{p}.side", table=SIDE_TABLE, table_width=self.side_dim * len(self.layers),
                                      col=i * self.side_dim, dim=self.side_dim, hidden_size=w, vocab_size=self.vocab, eps=eps)
             blocks.append(BlockSpec(kind="prenorm", norm1=norm(f"{p}.norm1"), mixer=mixer,
-                                    norm2=norm(f"{p}.norm2") if ff is not None else None, feed_forward=ff,
+                                    norm2=norm(f"{p}.norm2"), feed_forward=ff,
                                     residual_mult=self.residual_mult, side=side))
         emb = EmbeddingSpec("embed", self.vocab, w, suffix="")
         if self.pair_buckets:

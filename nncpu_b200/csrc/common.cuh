@@ -115,7 +115,7 @@ struct NormFusion {
 };
 
 constexpr int kActNone = 0, kActXielu = 1;
-constexpr int kActRelu2 = 4;      // the square of relu (plain epilogue, like xIELU; no numbers of its own)
+constexpr int kActRelu2 = 4;      // act_a times the square of relu (plain epilogue, like xIELU)
 // with the gated epilogue (act(gate) * up; kActNone there is silu(g) u): the tanh form of GELU, and the clamped
 // g sigmoid(1.702 g) (u + 1) with its limit in act_a
 constexpr int kActGateGelu = 2, kActGateSwishClamp = 3;
@@ -125,11 +125,11 @@ __device__ __forceinline__ float xielu_f(float z, float a, float b) {
     return z > 0.0f ? fmaf(a * z, z, 0.5f * z) : fmaf(b, expm1f(z) - z, 0.5f * z);
 }
 
-// An activation of the plain epilogue by its code: xIELU, or the square of relu.
+// An activation of the plain epilogue by its code: xIELU, or a times the square of relu.
 __device__ __forceinline__ float plain_act_f(float z, int act, float a, float b) {
     if (act == kActRelu2) {
         const float r = fmaxf(z, 0.0f);
-        return r * r;
+        return (r * r) * a;
     }
     return act == kActXielu ? xielu_f(z, a, b) : z;
 }

@@ -2350,10 +2350,69 @@ layernorm_kernel(const float* __restrict__ x, const void* __restrict__ w, const 
     }
 }
 
+// The common case, rows of a width that is a multiple of 4 and at most 256 * 4 * kVec: every thread keeps its part of
+// the row in registers between the mean, the deviations and the scaling, so the row is read once, 16 bytes at a time.
+template <int kVec>
+__global__ void __launch_bounds__(256)
+layernorm_f32_kernel(const float* __restrict__ x, const void* __restrict__ w, const void* __restrict__ b, int p_dt,
+                     void* __restrict__ y, int y_dt, const int* __restrict__ rows, int dim, float eps) {
+    __shared__ float scratch[33];
+    const int r_out = blockIdx.x;
+    const int r_in = rows ? rows[r_out] : r_out;
+    const int n4 = dim >> 2;
+    float4 v[kVec];
+    float s = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) {
+        const int i = threadIdx.x + j * 256;
+        v[j] = (r_in >= 0 && i < n4) ? reinterpret_cast<const float4*>(x + (size_t)r_in * dim)[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        s += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+    }
+    const float mean = block_sum(s, scratch) * (1.0f / (float)dim);
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) {
+        if (threadIdx.x + j * 256 >= n4) continue;
+        v[j].x -= mean; v[j].y -= mean; v[j].z -= mean; v[j].w -= mean;
+        ss = fmaf(v[j].x, v[j].x, ss); ss = fmaf(v[j].y, v[j].y, ss);
+        ss = fmaf(v[j].z, v[j].z, ss); ss = fmaf(v[j].w, v[j].w, ss);
+    }
+    const float scale = r_in >= 0 ? 1.0f / sqrtf(block_sum(ss, scratch) * (1.0f / (float)dim) + eps) : 0.0f;
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) {
+        const int i = threadIdx.x + j * 256;
+        if (i >= n4) continue;
+        float o[4] = {v[j].x * scale, v[j].y * scale, v[j].z * scale, v[j].w * scale};
+        if (r_in >= 0) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                if (w) o[e] *= ld_f(w, 4 * i + e, p_dt);
+                if (b) o[e] += ld_f(b, 4 * i + e, p_dt);
+            }
+        }
+        const size_t at = (size_t)r_out * dim + 4 * i;
+        if (y_dt == DT_BF16) {
+            __nv_bfloat162 h[2] = {__floats2bfloat162_rn(o[0], o[1]), __floats2bfloat162_rn(o[2], o[3])};
+            *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(y) + at) = *reinterpret_cast<uint2*>(h);
+        } else {
+            *reinterpret_cast<float4*>(reinterpret_cast<float*>(y) + at) = make_float4(o[0], o[1], o[2], o[3]);
+        }
+    }
+}
+
 extern "C" int nncpu_layernorm(const float* x, const void* w, const void* b, int p_dt, void* y, int y_dt,
                                const int* rows, int n_rows, int dim, float eps, void* stream) {
     NN_CHECK(n_rows >= 0 && dim > 0, "layernorm: %d rows of %d", n_rows, dim);
     if (n_rows == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dim % 4 == 0 && dim <= 256 * 4 * 8 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)y % 16) == 0) {
+        if (dim <= 1024) layernorm_f32_kernel<1><<<n_rows, 256, 0, st>>>(x, w, b, p_dt, y, y_dt, rows, dim, eps);
+        else if (dim <= 2048) layernorm_f32_kernel<2><<<n_rows, 256, 0, st>>>(x, w, b, p_dt, y, y_dt, rows, dim, eps);
+        else if (dim <= 4096) layernorm_f32_kernel<4><<<n_rows, 256, 0, st>>>(x, w, b, p_dt, y, y_dt, rows, dim, eps);
+        else layernorm_f32_kernel<8><<<n_rows, 256, 0, st>>>(x, w, b, p_dt, y, y_dt, rows, dim, eps);
+        NN_LAUNCH_OK("layernorm");
+        return 0;
+    }
     layernorm_kernel<<<n_rows, 256, 0, (cudaStream_t)stream>>>(x, w, b, p_dt, y, y_dt, rows, dim, eps);
     NN_LAUNCH_OK("layernorm");
     return 0;
@@ -2471,28 +2530,88 @@ branch_norm_add_kernel(float* __restrict__ x, const float* __restrict__ a, const
     }
 }
 
+// The common case, rows of a width that is a multiple of 4 and at most 256 * 4 * kVec: the branches' rows stay in
+// registers between the sums of squares and the scaling, so every row is read once.
+template <int kVec, bool kTwo>
+__global__ void __launch_bounds__(256)
+branch_norm_add_f32_kernel(float* __restrict__ x, const float* __restrict__ a, const void* __restrict__ wa,
+                           const float* __restrict__ b, const void* __restrict__ wb, int w_dt, float eps, float alpha, int dim) {
+    __shared__ float scratch[33];
+    const size_t base = (size_t)blockIdx.x * dim;
+    const int n4 = dim >> 2;
+    float4 va[kVec], vb[kTwo ? kVec : 1];
+    float sa = 0.0f, sb = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) {
+        const int i = threadIdx.x + j * 256;
+        va[j] = i < n4 ? reinterpret_cast<const float4*>(a + base)[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        sa = fmaf(va[j].x, va[j].x, sa); sa = fmaf(va[j].y, va[j].y, sa);
+        sa = fmaf(va[j].z, va[j].z, sa); sa = fmaf(va[j].w, va[j].w, sa);
+        if (kTwo) {
+            vb[j] = i < n4 ? reinterpret_cast<const float4*>(b + base)[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            sb = fmaf(vb[j].x, vb[j].x, sb); sb = fmaf(vb[j].y, vb[j].y, sb);
+            sb = fmaf(vb[j].z, vb[j].z, sb); sb = fmaf(vb[j].w, vb[j].w, sb);
+        }
+    }
+    const float ra = 1.0f / sqrtf(block_sum(sa, scratch) * (1.0f / (float)dim) + eps);
+    const float rb = kTwo ? 1.0f / sqrtf(block_sum(sb, scratch) * (1.0f / (float)dim) + eps) : 0.0f;
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) {
+        const int i = threadIdx.x + j * 256;
+        if (i >= n4) continue;
+        const float pa[4] = {va[j].x, va[j].y, va[j].z, va[j].w};
+        float4 was = reinterpret_cast<float4*>(x + base)[i];
+        float o[4] = {was.x, was.y, was.z, was.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            float v = (pa[e] * ra) * (wa ? ld_f(wa, 4 * i + e, w_dt) : 1.0f);
+            if (kTwo) {
+                const float pb = e == 0 ? vb[j].x : e == 1 ? vb[j].y : e == 2 ? vb[j].z : vb[j].w;
+                v += (pb * rb) * (wb ? ld_f(wb, 4 * i + e, w_dt) : 1.0f);
+            }
+            o[e] = fmaf(alpha, v, o[e]);
+        }
+        reinterpret_cast<float4*>(x + base)[i] = make_float4(o[0], o[1], o[2], o[3]);
+    }
+}
+
 extern "C" int nncpu_branch_norm_add(float* x, const float* a, const void* wa, const float* b, const void* wb, int w_dt,
                                      float eps, float alpha, int n_tok, int dim, void* stream) {
     NN_CHECK(n_tok >= 0 && dim > 0 && a != nullptr, "branch norm: %d rows of %d", n_tok, dim);
     if (n_tok == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dim % 4 == 0 && dim <= 256 * 4 * 8 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)a % 16) == 0 && ((uintptr_t)b % 16) == 0) {
+#define NN_BRANCH(V)                                                                                                  \
+        do {                                                                                                          \
+            if (b) branch_norm_add_f32_kernel<V, true><<<n_tok, 256, 0, st>>>(x, a, wa, b, wb, w_dt, eps, alpha, dim);  \
+            else branch_norm_add_f32_kernel<V, false><<<n_tok, 256, 0, st>>>(x, a, wa, b, wb, w_dt, eps, alpha, dim);   \
+        } while (0)
+        if (dim <= 1024) NN_BRANCH(1);
+        else if (dim <= 2048) NN_BRANCH(2);
+        else if (dim <= 4096) NN_BRANCH(4);
+        else NN_BRANCH(8);
+#undef NN_BRANCH
+        NN_LAUNCH_OK("branch norm");
+        return 0;
+    }
     branch_norm_add_kernel<<<n_tok, 256, 0, (cudaStream_t)stream>>>(x, a, wa, b, wb, w_dt, eps, alpha, dim);
     NN_LAUNCH_OK("branch norm");
     return 0;
 }
 
 // ---------------------------------------------------------------------------
-// Elementwise activations of one product's 32-bit result: kind 0 the square of relu.
+// Elementwise activations of one product's 32-bit result: kind 0 `a` times the square of relu.
 // ---------------------------------------------------------------------------
-__global__ void unary_act_kernel(const float* __restrict__ x, void* __restrict__ out, int out_dt, long n, int kind) {
+__global__ void unary_act_kernel(const float* __restrict__ x, void* __restrict__ out, int out_dt, long n, int kind, float a) {
     const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= n) return;
-    st_f(out, (size_t)idx, out_dt, plain_act_f(x[idx], kind == 0 ? kActRelu2 : kActNone, 0.0f, 0.0f));
+    st_f(out, (size_t)idx, out_dt, plain_act_f(x[idx], kind == 0 ? kActRelu2 : kActNone, a, 0.0f));
 }
 
-extern "C" int nncpu_unary_act(const float* x, void* out, int out_dt, long n, int kind, void* stream) {
+extern "C" int nncpu_unary_act(const float* x, void* out, int out_dt, long n, int kind, float a, void* stream) {
     NN_CHECK(n >= 0 && kind == 0, "activation: %ld elements, kind %d", n, kind);
     if (n == 0) return 0;
-    unary_act_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, out, out_dt, n, kind);
+    unary_act_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, out, out_dt, n, kind, a);
     NN_LAUNCH_OK("activation");
     return 0;
 }
@@ -2510,6 +2629,68 @@ __global__ void token_gate_kernel(const float* __restrict__ z, const void* __res
     const int j = (int)(idx % dim), id = ids[t];
     const float e = id >= 0 ? ld_f(table, (size_t)id * ld + col + j, table_dt) : 0.0f;
     st_f(out, (size_t)idx, out_dt, gelu_tanh_f(z[idx]) * e);
+}
+
+// The same for a step of a few tokens, with both products and the norm, in one launch: one block per token computes
+// z = W_gate x (a warp per row), g = gelu_tanh(z) * lanes, y = W_proj g (a thread per row), and
+// x <- x + alpha * y / sqrt(mean(y^2) + eps) * w.  x float32 [n_tok, width] is read as it is (not rounded).
+__global__ void __launch_bounds__(256)
+token_side_step_kernel(float* __restrict__ x, const void* __restrict__ w_gate, const void* __restrict__ w_proj,
+                       const void* __restrict__ w_norm, int w_dt, const void* __restrict__ table, int table_dt,
+                       const int* __restrict__ ids, int ld, int col, int width, int dim, float eps, float alpha) {
+    extern __shared__ float smem[];          // the token's row, then its gated lanes
+    __shared__ float scratch[33];
+    float* xs = smem;
+    float* g = smem + width;
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int id = ids[t];
+    for (int i = threadIdx.x; i < width; i += blockDim.x) xs[i] = x[(size_t)t * width + i];
+    __syncthreads();
+    for (int j = warp; j < dim; j += 8) {
+        const float z = warp_dot(w_gate, (size_t)j * width, w_dt, xs, width, lane);
+        if (lane == 0) g[j] = id >= 0 ? gelu_tanh_f(z) * ld_f(table, (size_t)id * ld + col + j, table_dt) : 0.0f;
+    }
+    __syncthreads();
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float acc = 0.0f;
+        if (w_dt == DT_BF16 && (dim & 7) == 0) {
+            const uint4* row = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(w_proj) + (size_t)i * dim);
+            for (int c = 0; c < dim >> 3; ++c) {
+                const uint4 v = row[c];
+                const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float2 f = __bfloat1622float2(h2[k]);
+                    acc = fmaf(f.x, g[8 * c + 2 * k], acc);
+                    acc = fmaf(f.y, g[8 * c + 2 * k + 1], acc);
+                }
+            }
+        } else {
+            for (int j = 0; j < dim; ++j) acc = fmaf(ld_f(w_proj, (size_t)i * dim + j, w_dt), g[j], acc);
+        }
+        xs[i] = acc;                          // the thread's own place: nobody else reads the token's row any more
+        ss = fmaf(acc, acc, ss);
+    }
+    const float scale = alpha / sqrtf(block_sum(ss, scratch) * (1.0f / (float)width) + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+        x[(size_t)t * width + i] += (xs[i] * scale) * ld_f(w_norm, i, w_dt);
+}
+
+extern "C" int nncpu_token_side_step_fits(int width, int dim) {
+    return width > 0 && dim > 0 && (size_t)(width + dim) * 4 <= 48 * 1024;
+}
+
+extern "C" int nncpu_token_side_step(float* x, const void* w_gate, const void* w_proj, const void* w_norm, int w_dt,
+                                     const void* table, int table_dt, const int* ids, int ld, int col, int n_tok, int width,
+                                     int dim, float eps, float alpha, void* stream) {
+    NN_CHECK(n_tok >= 0 && nncpu_token_side_step_fits(width, dim) && col >= 0 && col + dim <= ld,
+             "token input: %d tokens of %d, lanes %d..%d of %d", n_tok, width, col, col + dim, ld);
+    if (n_tok == 0) return 0;
+    token_side_step_kernel<<<n_tok, 256, (size_t)(width + dim) * 4, (cudaStream_t)stream>>>(
+        x, w_gate, w_proj, w_norm, w_dt, table, table_dt, ids, ld, col, width, dim, eps, alpha);
+    NN_LAUNCH_OK("token input");
+    return 0;
 }
 
 extern "C" int nncpu_token_gate(const float* z, const void* table, int table_dt, const int* ids, int ld, int col,

@@ -241,12 +241,12 @@ extern "C" int nncpu_gla_scan(const float* proj, int row, const float* z, float*
 
 // The mixer's output stage: every head's o is divided by its root mean square over the e value channels (eps
 // inside the root), multiplied by the weight w [e] that the heads share (null: ones) and by silu(g), the gate of its
-// channel (gate_kind 1: by sigmoid(g)).
+// channel (gate_kind 1: by sigmoid(g)), and by out_scale.
 // One warp per (token, head); out [n_tok, H*e] in the run's element type.
 __global__ void __launch_bounds__(256)
 gla_output_kernel(const float* __restrict__ o, const float* __restrict__ proj, int row, int g_at,
                   const void* __restrict__ w, int w_dt, float eps, void* __restrict__ out, int out_dt, long n_items,
-                  int H, int e, int gate_kind) {
+                  int H, int e, int gate_kind, float out_scale) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long item = (long)blockIdx.x * 8 + warp;
     if (item >= n_items) return;
@@ -256,7 +256,7 @@ gla_output_kernel(const float* __restrict__ o, const float* __restrict__ proj, i
     float ss = 0.0f;
     for (int j = lane; j < e; j += 32) ss = fmaf(src[j], src[j], ss);
     ss = warp_sum(ss);
-    const float scale = 1.0f / sqrtf(ss * (1.0f / (float)e) + eps);
+    const float scale = out_scale / sqrtf(ss * (1.0f / (float)e) + eps);
     const float* g = proj + (size_t)t * row + g_at + (size_t)h * e;
     for (int j = lane; j < e; j += 32) {
         const float gate = g[j];
@@ -267,12 +267,13 @@ gla_output_kernel(const float* __restrict__ o, const float* __restrict__ proj, i
 }
 
 extern "C" int nncpu_gla_output(const float* o, const float* proj, int row, int g_at, const void* w, int w_dt,
-                                float eps, void* out, int out_dt, int n_tok, int H, int e, int gate_kind, void* stream) {
+                                float eps, void* out, int out_dt, int n_tok, int H, int e, int gate_kind, float out_scale,
+                                void* stream) {
     NN_CHECK(n_tok >= 0 && H > 0 && e > 0 && g_at >= 0 && g_at + H * e <= row, "gla_output: sizes");
     if (n_tok == 0) return 0;
     const long n_items = (long)n_tok * H;
     gla_output_kernel<<<(unsigned)((n_items + 7) / 8), 256, 0, (cudaStream_t)stream>>>(o, proj, row, g_at, w, w_dt, eps,
-                                                                                       out, out_dt, n_items, H, e, gate_kind);
+                                                                                       out, out_dt, n_items, H, e, gate_kind, out_scale);
     NN_LAUNCH_OK("gla_output");
     return 0;
 }
@@ -287,7 +288,7 @@ __global__ void __launch_bounds__(kThreads)
 gla_step_kernel(const float* __restrict__ proj, int row, const float* __restrict__ z, float* __restrict__ state,
                 const int* __restrict__ seq_slots, const void* __restrict__ w, int w_dt, float eps,
                 void* __restrict__ out, int out_dt, int H, int d, int e, float q_scale, float inv_tau,
-                const float* __restrict__ head_decay) {
+                const float* __restrict__ head_decay, const float* __restrict__ cos_sin, int half, float k_scale) {
     extern __shared__ float4 akq[];          // d entries of (a, k, q, -)
     __shared__ float scratch[33];
     const int t = blockIdx.x, h = blockIdx.y, j = threadIdx.x;
@@ -298,9 +299,22 @@ gla_step_kernel(const float* __restrict__ proj, int row, const float* __restrict
         return;
     }
     const float* p = proj + (size_t)t * row;
-    for (int i = j; i < d; i += blockDim.x)
+    for (int i = j; i < d; i += blockDim.x) {
+        const float* qp = p + (size_t)h * d;
+        const float* kp = qp + (size_t)H * d;
+        float qv = qp[i], kv = kp[i];
+        if (cos_sin != nullptr && i < 2 * half) {
+            // retention: q and k are rotated by the token's position on the way in (the pair (u, v) = lanes (i, i + half)
+            // becomes (u c - v s, v c + u s)), with the operations of the kernel that rotates a prompt's rows in place
+            const int ii = i < half ? i : i - half;
+            const float c = cos_sin[((size_t)t * half + ii) * 2], sn = cos_sin[((size_t)t * half + ii) * 2 + 1];
+            const float qo = qp[i < half ? i + half : i - half], ko = kp[i < half ? i + half : i - half];
+            qv = i < half ? qv * c - qo * sn : qv * c + qo * sn;
+            kv = i < half ? kv * c - ko * sn : kv * c + ko * sn;
+        }
         akq[i] = make_float4(head_decay ? head_decay[h] : expf(log_sigmoid_f(z[(size_t)t * H * d + (size_t)h * d + i]) * inv_tau),
-                             p[(size_t)H * d + (size_t)h * d + i], p[(size_t)h * d + i] * q_scale, 0.0f);
+                             kv * k_scale, qv * q_scale, 0.0f);
+    }
     __syncthreads();
     float acc = 0.0f;
     if (j < e) {
@@ -338,7 +352,10 @@ gla_step_kernel(const float* __restrict__ proj, int row, const float* __restrict
 
 extern "C" int nncpu_gla_step(const float* proj, int row, const float* z, float* state, const int* seq_slots,
                               const void* w, int w_dt, float eps, void* out, int out_dt, int n_tok, int H, int d, int e,
-                              float q_scale, float tau, const float* head_decay, void* stream) {
+                              float q_scale, float tau, const float* head_decay, const float* cos_sin, int half, float k_scale,
+                              void* stream) {
+    // cos_sin [n_tok, half, 2] (optional): q and k are rotated on the way in; k is multiplied by k_scale (1: as it is)
+    NN_CHECK(cos_sin == nullptr || (half > 0 && 2 * half <= d), "gla_step: %d rotated lanes of %d", 2 * half, d);
     NN_CHECK(n_tok >= 0 && H > 0 && H <= 65535 && d > 0 && e > 0, "gla_step: %d tokens, %d heads of %d x %d", n_tok, H, d, e);
     NN_CHECK(e <= 1024, "gla_step: %d value channels a head (at most 1024)", e);
     NN_CHECK(d <= 2048, "gla_step: %d key channels a head (at most 2048)", d);
@@ -354,13 +371,13 @@ extern "C" int nncpu_gla_step(const float* proj, int row, const float* z, float*
     // fill the waits (batch 8 of 8 heads 20 -> 11 us with 32; batch 64 of 16 heads 57 us with 8, 78 with 32)
     if (threads <= 256 && (long)n_tok * H <= 2L * sms)
         gla_step_kernel<256, 32><<<dim3(n_tok, H), threads, (size_t)d * sizeof(float4), (cudaStream_t)stream>>>(
-            proj, row, z, state, seq_slots, w, w_dt, eps, out, out_dt, H, d, e, q_scale, 1.0f / tau, head_decay);
+            proj, row, z, state, seq_slots, w, w_dt, eps, out, out_dt, H, d, e, q_scale, 1.0f / tau, head_decay, cos_sin, half, k_scale);
     else if (threads <= 256)
         gla_step_kernel<256, 8><<<dim3(n_tok, H), threads, (size_t)d * sizeof(float4), (cudaStream_t)stream>>>(
-            proj, row, z, state, seq_slots, w, w_dt, eps, out, out_dt, H, d, e, q_scale, 1.0f / tau, head_decay);
+            proj, row, z, state, seq_slots, w, w_dt, eps, out, out_dt, H, d, e, q_scale, 1.0f / tau, head_decay, cos_sin, half, k_scale);
     else
         gla_step_kernel<1024, 8><<<dim3(n_tok, H), threads, (size_t)d * sizeof(float4), (cudaStream_t)stream>>>(
-            proj, row, z, state, seq_slots, w, w_dt, eps, out, out_dt, H, d, e, q_scale, 1.0f / tau, head_decay);
+            proj, row, z, state, seq_slots, w, w_dt, eps, out, out_dt, H, d, e, q_scale, 1.0f / tau, head_decay, cos_sin, half, k_scale);
     NN_LAUNCH_OK("gla_step");
     return 0;
 }
@@ -425,8 +442,8 @@ __device__ __forceinline__ float softplus_r(float z) { return fmaxf(z, 0.0f) + l
 constexpr float kUnitEps = 1e-6f;     // inside the root that makes q and k unit vectors
 constexpr int kMaxTaps = 32;
 
-// One warp per (token, item): G query heads, G key heads, H value heads, and one item for the token's H decays and
-// write strengths.  xc [n_tok, C] receives the convolved, activated (and for q, k: normalised) channels, gb [n_tok,
+// One warp per (token, item): G query heads, G key heads, H value heads, one item for the token's H decays and
+// write strengths, and (with a decay per key channel) H more items, one per head's d decays.  xc [n_tok, C] receives the convolved, activated (and for q, k: normalised) channels, gb [n_tok,
 // 2 H] the decays g and then the strengths beta.  A token of no sequence (tok_seq < 0) gets zeros.  With kShiftHere
 // (every sequence of the step brings ONE token, so a channel's kept inputs are read by one lane of one warp alone) that
 // lane also advances the channel's kept inputs by the token, which saves the launch of the kernel below.
@@ -441,12 +458,19 @@ delta_prepare_kernel(const float* __restrict__ proj, int ld, const void* __restr
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long item = (long)blockIdx.x * 8 + warp;
     if (item >= n_items) return;
-    const int per_tok = 2 * G + H + 1;
+    const int per_tok = 2 * G + H + 1 + (chan_z ? H : 0);
     const int t = (int)(item / per_tok), it = (int)(item % per_tok);
     const int C = 2 * G * d + H * e;
     const int seq = tok_seq[t];
     const int slot = seq < 0 ? -1 : seq_slots[seq];
-    if (it == per_tok - 1) {
+    if (it > 2 * G + H) {       // (a decay per key channel) one more item per head: its d decays from their logits, in place
+        const int h = it - (2 * G + H + 1);
+        float* zz = chan_z + ((size_t)t * H + h) * d;
+        const float rate = expf(ld_f(a_log, h, p_dt));
+        for (int i = lane; i < d; i += 32) zz[i] = slot >= 0 ? expf(0.0f - rate * softplus_r(zz[i])) : 0.0f;
+        return;
+    }
+    if (it == 2 * G + H) {
         for (int h = lane; h < H; h += 32) {
             float g = 0.0f, beta = 0.0f;
             if (slot >= 0) {
@@ -456,11 +480,6 @@ delta_prepare_kernel(const float* __restrict__ proj, int ld, const void* __restr
             }
             gb[(size_t)t * 2 * H + h] = g;
             gb[(size_t)t * 2 * H + H + h] = beta;
-        }
-        if (chan_z) {       // a decay per head and key channel, from its logit (the bias is in it already), in place
-            float* zz = chan_z + (size_t)t * H * d;
-            for (int i = lane; i < H * d; i += 32)
-                zz[i] = slot >= 0 ? expf(0.0f - expf(ld_f(a_log, i / d, p_dt)) * softplus_r(zz[i])) : 0.0f;
         }
         return;
     }
@@ -532,7 +551,7 @@ extern "C" int nncpu_delta_prepare(const float* proj, int ld, const void* conv_w
     const int C = 2 * G * d + H * e;
     NN_CHECK(beta_col >= C && ld >= beta_col + (chan_z ? 1 : 2) * H, "delta prepare: rows of %d floats", ld);
     if (n_tok == 0) return 0;
-    const long n_items = (long)n_tok * (2 * G + H + 1);
+    const long n_items = (long)n_tok * (2 * G + H + 1 + (chan_z ? H : 0));
     if (one_token_each)
         delta_prepare_kernel<true><<<(unsigned)((n_items + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
             proj, ld, conv_w, w_dt, conv_state, slot_stride, tok_seq, seq_slots, cu_seqlens, a_log, dt_bias, p_dt, xc, gb, n_items, H,
@@ -587,7 +606,9 @@ delta_scan_kernel(const float* __restrict__ xc, const float* __restrict__ gb, co
     constexpr int CW = CPL * 32 / R;                // columns a warp: CPL neighbouring ones a lane
     constexpr int COLS = 4 * CW;                    // columns a block
     constexpr int TB = delta_group(DP, CH);         // tokens a group
-    constexpr int BUF = TB * ((CH ? 3 : 2) * DP + COLS + 2);   // floats a buffer: k, q (, decays) [TB][DP], v [TB][COLS], (g, beta) [TB]
+    // floats a buffer: k, q (, decays) [TB][DP], v [TB][COLS], (g, beta) [TB]; a whole number of 16-byte pieces, so that
+    // the second buffer's rows of k, q and decays start on 16-byte borders like the first one's
+    constexpr int BUF = (TB * ((CH ? 3 : 2) * DP + COLS + 2) + 3) / 4 * 4;
     extern __shared__ __align__(16) float dsm_[];
     const int seq = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31, r = lane % R;
@@ -621,10 +642,10 @@ delta_scan_kernel(const float* __restrict__ xc, const float* __restrict__ gb, co
         const int nt = min(TB, t1 - g0);
         float* kb = dsm_ + buf * BUF;
         float* qb = kb + TB * DP;
-        float* vb = qb + TB * DP;
+        float* gcb = qb + TB * DP;                   // (CH) the tokens' decays per key channel
+        float* vb = gcb + (CH ? TB * DP : 0);
         float* gbb = vb + TB * COLS;
         if (CH) {
-            float* gcb = gbb + TB * 2;
             const bool wide_g = (d & 3) == 0 && (reinterpret_cast<uintptr_t>(gch) & 15) == 0;
             if (wide_g) {
                 const int d4 = d >> 2;
@@ -675,9 +696,9 @@ delta_scan_kernel(const float* __restrict__ xc, const float* __restrict__ gb, co
         const int nt = min(TB, t1 - g0);
         const float* kb = dsm_ + buf * BUF;
         const float* qb = kb + TB * DP;
-        const float* vb = qb + TB * DP;
+        const float* gcb = qb + TB * DP;             // (CH) the tokens' decays per key channel
+        const float* vb = gcb + (CH ? TB * DP : 0);
         const float* gbb = vb + TB * COLS;
-        const float* gcb = gbb + TB * 2;             // (CH) the tokens' decays per key channel
         // One token: the chain from token to token is S^T k (DR multiply-adds in four sums, log2(R) shuffles), u, and
         // the update of S, once per column of the lane: the lane's columns are independent chains that share the
         // loads of k and q and fill one another's waits.  The lane's parts of o = S^T q are left in os; their sums
@@ -788,8 +809,8 @@ template <int DR, int R, int CPL>
 static int launch_delta_scan(const float* xc, const float* gb, const float* gch, float* state, long slot_stride, const int* seq_slots, const int* cu_seqlens,
                              float* o, int n_seqs, int H, int G, int d, int e, cudaStream_t st) {
     constexpr int DP = DR * R, COLS = 4 * (CPL * 32 / R);
-    constexpr size_t smem = (size_t)2 * delta_group(DP, false) * (2 * DP + COLS + 2) * sizeof(float);
-    constexpr size_t smem_ch = (size_t)2 * delta_group(DP, true) * (3 * DP + COLS + 2) * sizeof(float);
+    constexpr size_t smem = (size_t)2 * ((delta_group(DP, false) * (2 * DP + COLS + 2) + 3) / 4 * 4) * sizeof(float);
+    constexpr size_t smem_ch = (size_t)2 * ((delta_group(DP, true) * (3 * DP + COLS + 2) + 3) / 4 * 4) * sizeof(float);
     static_assert(smem <= 48 * 1024 && smem_ch <= 48 * 1024, "the staging buffers fit the default shared memory");
     dim3 grid(n_seqs, H, (e + COLS - 1) / COLS);
     if (gch != nullptr)

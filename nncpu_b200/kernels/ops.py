@@ -202,10 +202,29 @@ def branch_norm_add(x, a, wa, b, wb, eps: float, alpha: float) -> None:
           _f(alpha), _i(n), _i(dim), _stream())
 
 
-def relu2(x, out) -> None:
-    """out = max(x, 0)^2; x float32."""
+def relu2(x, out, scale: float = 1.0) -> None:
+    """out = scale * max(x, 0)^2; x float32."""
     assert x.dtype == torch.float32 and x.shape == out.shape and x.is_contiguous() and out.is_contiguous()
-    _call("generic", "nncpu_unary_act", _ptr(x), _ptr(out), _i(_code(out)), _l(x.numel()), _i(0), _stream())
+    _call("generic", "nncpu_unary_act", _ptr(x), _ptr(out), _i(_code(out)), _l(x.numel()), _i(0), _f(scale), _stream())
+
+
+def token_side_step_fits(width: int, dim: int) -> bool:
+    """Whether ``token_side_step`` takes these sizes (a token's row and its gated lanes in one block's shared memory)."""
+    return width > 0 and dim > 0 and (width + dim) * 4 <= 48 * 1024
+
+
+def token_side_step(x, w_gate, w_proj, w_norm, table, ids, col: int, eps: float, alpha: float) -> None:
+    """x[t] += alpha * rmsnorm(W_proj (gelu_tanh(W_gate x[t]) * table[ids[t], col : col + dim])) * w_norm, for a step of
+    a few tokens in one launch; x float32, read as it is."""
+    n, width = x.shape
+    dim = w_gate.shape[0]
+    assert x.dtype == torch.float32 and x.is_contiguous() and w_gate.shape == (dim, width) and w_proj.shape == (width, dim)
+    assert w_gate.dtype == w_proj.dtype == w_norm.dtype and w_norm.numel() == width
+    assert w_gate.is_contiguous() and w_proj.is_contiguous()
+    assert table.dim() == 2 and table.is_contiguous() and ids.dtype == torch.int32 and ids.numel() >= n
+    _call("generic", "nncpu_token_side_step", _ptr(x), _ptr(w_gate), _ptr(w_proj), _ptr(w_norm), _i(_code(w_gate)),
+          _ptr(table), _i(_code(table)), _ptr(ids), _i(table.shape[1]), _i(col), _i(n), _i(width), _i(dim), _f(eps),
+          _f(alpha), _stream())
 
 
 def token_gate(z, table, ids, col: int, out) -> None:
@@ -270,7 +289,7 @@ _ACTIVATIONS = {"xielu": 1, "gelu_tanh": 2, "swish_clamp": 3, "relu2": 4}
 
 def _activation(activation):
     """``activation`` None, or (kind, a, b).  With the plain epilogue ("xielu", a, b), a = softplus(p) and
-    b = 1/2 + softplus(q) ready-made, or ("relu2", 0, 0), the square of relu: applied to the product's result after
+    b = 1/2 + softplus(q) ready-made, or ("relu2", a, 0), a times the square of relu: applied to the product's result after
     the bias (no accumulation).  With the
     gated epilogue the gate's activation in place of SiLU: ("gelu_tanh", 0, 0) or ("swish_clamp", limit, 0), see
     ``gated_act``."""
@@ -855,11 +874,12 @@ def gla_decay(z, tau: float) -> None:
 
 
 def gla_step(proj, z, state, seq_slots, weight, eps: float, out, n_heads: int, d: int, e: int, q_scale: float,
-             tau: float, head_decay=None) -> None:
+             tau: float, head_decay=None, cos_sin=None, k_scale: float = 1.0) -> None:
     """A decode step of gated linear attention, one token per sequence: the recurrence on ``state`` (as ``gla_scan``
     with sequences of one token, ``z`` holding logits), then the heads' norm, weight and gate (as ``gla_output``),
     in one launch.  ``out`` [n, H e] in float32 or bfloat16.  ``head_decay`` (float32 [H]): one fixed decay per head
-    in place of the decays from ``z`` (which may then be None); ``weight`` None: ones."""
+    in place of the decays from ``z`` (which may then be None); ``weight`` None: ones.  ``cos_sin`` (float32
+    [n, half, 2]): q and k are rotated on the way in as ``retention_prepare`` rotates them; k is multiplied by ``k_scale``."""
     n = out.shape[0]
     assert proj.dtype == state.dtype == torch.float32 and (z is None or z.dtype == torch.float32)
     assert proj.shape == (n, 2 * n_heads * (d + e)) and out.shape == (n, n_heads * e)
@@ -870,7 +890,8 @@ def gla_step(proj, z, state, seq_slots, weight, eps: float, out, n_heads: int, d
     assert seq_slots.dtype == torch.int32 and seq_slots.numel() >= n
     _call("recurrent", "nncpu_gla_step", _ptr(proj), _i(proj.shape[1]), _ptr(z), _ptr(state), _ptr(seq_slots),
           _ptr(weight), _i(_code(weight)), _f(eps), _ptr(out), _i(_code(out)), _i(n), _i(n_heads), _i(d), _i(e),
-          _f(q_scale), _f(tau), _ptr(head_decay), _stream())
+          _f(q_scale), _f(tau), _ptr(head_decay), _ptr(cos_sin), _i(0 if cos_sin is None else cos_sin.shape[1]),
+          _f(k_scale), _stream())
 
 
 def gla_scan_force_columns(cpl: int) -> None:
@@ -902,17 +923,17 @@ OUTPUT_GATES = {"silu": 0, "sigmoid": 1}
 
 
 def gla_output(o, proj, weight, eps: float, out, n_heads: int, d: int, e: int, gate_col: int = -1,
-               gate: str = "silu") -> None:
+               gate: str = "silu", out_scale: float = 1.0) -> None:
     """out[t, h] = o[t, h] / rms(o[t, h]) * weight * silu(g[t, h]) with g the H e lanes of ``proj``'s rows from column
     ``gate_col`` (default: after 2 H d + H e lanes, where gated linear attention keeps them).  ``weight`` None: ones;
-    ``gate`` "sigmoid": sigmoid(g) in place of silu(g)."""
+    ``gate`` "sigmoid": sigmoid(g) in place of silu(g); the whole times ``out_scale``."""
     n = o.shape[0]
     assert o.dtype == proj.dtype == torch.float32 and o.shape == (n, n_heads * e) and out.shape == o.shape
     assert weight is None or weight.numel() == e
     _call("recurrent", "nncpu_gla_output", _ptr(o), _ptr(proj), _i(proj.shape[1]),
           _i(gate_col if gate_col >= 0 else 2 * n_heads * d + n_heads * e),
           _ptr(weight), _i(_code(weight)), _f(eps), _ptr(out), _i(_code(out)), _i(n), _i(n_heads), _i(e),
-          _i(OUTPUT_GATES[gate]), _stream())
+          _i(OUTPUT_GATES[gate]), _f(out_scale), _stream())
 
 
 def retention_prepare(proj, cos_sin, n_heads: int, d: int, k_scale: float) -> None:

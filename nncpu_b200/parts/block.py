@@ -34,9 +34,13 @@ class PreNormBlock(Block):
         self.mult = float(spec.residual_mult)
         self.side = None if spec.side is None else TokenSide(spec.side)
         self._parts = tuple(p for p in (self.norm1, self.mixer, self.norm2, self.feed_forward, self.side) if p is not None)
+        # a layer without a feed-forward may still name its second norm: its tensors are then optional and not used
+        self._spare = (base.build("norm", spec.norm2).params()
+                       if (self.feed_forward is None and spec.norm2 is not None) else [])
 
     def params(self):
-        return [p for part in self._parts for p in part.params()]
+        spare = [ParamSpec(p.name, p.shape, required=False, init=p.init) for p in self._spare]
+        return [p for part in self._parts for p in part.params()] + spare
 
     def bind(self, tensors, rt):
         self.rt = rt

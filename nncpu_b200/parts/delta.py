@@ -42,6 +42,7 @@ MAX_TAPS = 32
 @register_mixer("gated_delta")
 class GatedDelta(Mixer):
     accepts_deferred_norm = True    # x goes to Runtime.linear alone
+    scales_output = True            # ctx.out_scale rides on the heads' norm-and-gate stage, before the output product
 
     def __init__(self, spec, reads_other_cache: bool = False):
         if reads_other_cache:
@@ -156,7 +157,8 @@ class GatedDelta(Mixer):
                           flops=8.0 * n * H * d * e):
                 ops.delta_scan(xc, gb, cache.state, ctx.seq_slots, ctx.cu_seqlens, o, ctx.n_seqs, H, G, d, e, chan_g=z)
             with rt.phase("delta_gate"):
-                ops.gla_output(o, gate, self.w_norm, s.eps, gated, H, d, e, gate_col=0, gate="sigmoid")
+                ops.gla_output(o, gate, self.w_norm, s.eps, gated, H, d, e, gate_col=0, gate="sigmoid",
+                               out_scale=float(getattr(ctx, "out_scale", 1.0)))
             with rt.phase("delta_out", self.w_o, n):
                 rt.linear(gated, self.w_o, None, residual, accumulate=not getattr(ctx, "branch_is_fresh", False),
                           then_norm=getattr(ctx, "next_norm", None))
@@ -168,7 +170,8 @@ class GatedDelta(Mixer):
         with rt.phase("delta_scan", nbytes=state_bytes + 4.0 * (xc.numel() + o.numel()), flops=6.0 * n * H * d * e):
             ops.delta_scan(xc, gb, cache.state, ctx.seq_slots, ctx.cu_seqlens, o, ctx.n_seqs, H, G, d, e)
         with rt.phase("delta_gate"):
-            ops.gla_output(o, proj, self.w_norm, s.eps, gated, H, d, e, gate_col=self.gate_col)
+            ops.gla_output(o, proj, self.w_norm, s.eps, gated, H, d, e, gate_col=self.gate_col,
+                           out_scale=float(getattr(ctx, "out_scale", 1.0)))
         with rt.phase("delta_out", self.w_o, n):
             rt.linear(gated, self.w_o, None, residual, accumulate=not getattr(ctx, "branch_is_fresh", False),
                       then_norm=getattr(ctx, "next_norm", None))

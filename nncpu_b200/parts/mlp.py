@@ -229,6 +229,8 @@ class DenseMlp(FeedForward):
         if spec.activation not in ("xielu", "relu2"):
             raise UnsupportedModel(f"{spec.name}: activation {spec.activation!r} is not supported (supported: xielu, relu2)")
         self.spec = spec
+        # without biases a factor on the part's output can ride on the square of relu: down(a relu(z)^2) = a down(relu(z)^2)
+        self.scales_output = spec.activation == "relu2" and not spec.bias
 
     def params(self):
         s = self.spec
@@ -249,7 +251,7 @@ class DenseMlp(FeedForward):
         # two numbers enter as softplus(p) and 1/2 + softplus(q), worked out once here in 32-bit.
         self.fused = rt.tensor_cores_take(rt.dtype, self.w_up, s.hidden_size) and (self.act is None or not self.act.is_meta)
         if self.fused and s.activation == "relu2":
-            self.activation = ("relu2", 0.0, 0.0)
+            self.activation = ("relu2", 1.0, 0.0)
         elif self.fused:
             p, q = (math.log1p(math.exp(-abs(v))) + max(v, 0.0) for v in self.act.detach().float().tolist())   # softplus
             self.activation = ("xielu", p, 0.5 + q)
@@ -261,16 +263,18 @@ class DenseMlp(FeedForward):
         s, rt = self.spec, self.rt
         n = x.shape[0]
         act = rt.empty(n, s.intermediate_size)
+        scale = float(getattr(ctx, "out_scale", 1.0)) if self.scales_output else 1.0
         if self.fused:
             with rt.phase("ffn_up", self.w_up, n):
-                rt.linear(x, self.w_up, self.b_up, act, activation=self.activation)
+                rt.linear(x, self.w_up, self.b_up, act,
+                          activation=("relu2", scale, 0.0) if s.activation == "relu2" else self.activation)
         else:
             up = rt.empty(n, s.intermediate_size, dtype=torch.float32)
             with rt.phase("ffn_up", self.w_up, n):
                 rt.linear(x, self.w_up, self.b_up, up)
             with rt.phase("ffn_act"):
                 if s.activation == "relu2":
-                    ops.relu2(up, act)
+                    ops.relu2(up, act, scale)
                 else:
                     ops.xielu(up, self.act, act)
         with rt.phase("ffn_down", self.w_down, n):

@@ -81,17 +81,18 @@ class Retention(Mixer):
         proj = rt.empty(n, 2 * (self.qk_size + self.v_size), dtype=torch.float32)
         with rt.phase("ret_proj", self.w_qkvg, n):
             rt.linear(x, self.w_qkvg, None, proj)
-        with rt.phase("ret_rope", nbytes=16.0 * n * self.qk_size):
+        with rt.phase("ret_rope"):
             cos_sin = None if self.position is None else self.position.tables(ctx)
-            ops.retention_prepare(proj, cos_sin, H, d, d ** -0.5)
         gated = rt.empty(n, self.v_size)
         state_bytes = 8.0 * ctx.n_seqs * H * d * e                   # read and written once a step
         if ctx.is_decode and e <= 1024:
-            # one token per sequence: recurrence, norm and gate in one launch that streams the state once
+            # one token per sequence: rotation, recurrence, norm and gate in one launch that streams the state once
             with rt.phase("ret_scan", nbytes=state_bytes + 4.0 * proj.numel() + gated.numel() * gated.element_size()):
                 ops.gla_step(proj, None, cache.state, ctx.seq_slots, None, s.eps, gated, H, d, e, 1.0, 1.0,
-                             head_decay=self.decays)
+                             head_decay=self.decays, cos_sin=cos_sin, k_scale=d ** -0.5)
         else:
+            with rt.phase("ret_rope", nbytes=16.0 * n * self.qk_size):
+                ops.retention_prepare(proj, cos_sin, H, d, d ** -0.5)
             o = rt.empty(n, self.v_size, dtype=torch.float32)
             with rt.phase("ret_scan", nbytes=state_bytes + 4.0 * (proj.numel() + o.numel()), flops=4.0 * n * H * d * e):
                 ops.gla_scan(proj, None, cache.state, ctx.seq_slots, ctx.cu_seqlens, o, ctx.n_seqs, H, d, e, 1.0, 1.0,
