@@ -2631,68 +2631,6 @@ __global__ void token_gate_kernel(const float* __restrict__ z, const void* __res
     st_f(out, (size_t)idx, out_dt, gelu_tanh_f(z[idx]) * e);
 }
 
-// The same for a step of a few tokens, with both products and the norm, in one launch: one block per token computes
-// z = W_gate x (a warp per row), g = gelu_tanh(z) * lanes, y = W_proj g (a thread per row), and
-// x <- x + alpha * y / sqrt(mean(y^2) + eps) * w.  x float32 [n_tok, width] is read as it is (not rounded).
-__global__ void __launch_bounds__(256)
-token_side_step_kernel(float* __restrict__ x, const void* __restrict__ w_gate, const void* __restrict__ w_proj,
-                       const void* __restrict__ w_norm, int w_dt, const void* __restrict__ table, int table_dt,
-                       const int* __restrict__ ids, int ld, int col, int width, int dim, float eps, float alpha) {
-    extern __shared__ float smem[];          // the token's row, then its gated lanes
-    __shared__ float scratch[33];
-    float* xs = smem;
-    float* g = smem + width;
-    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int id = ids[t];
-    for (int i = threadIdx.x; i < width; i += blockDim.x) xs[i] = x[(size_t)t * width + i];
-    __syncthreads();
-    for (int j = warp; j < dim; j += 8) {
-        const float z = warp_dot(w_gate, (size_t)j * width, w_dt, xs, width, lane);
-        if (lane == 0) g[j] = id >= 0 ? gelu_tanh_f(z) * ld_f(table, (size_t)id * ld + col + j, table_dt) : 0.0f;
-    }
-    __syncthreads();
-    float ss = 0.0f;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        float acc = 0.0f;
-        if (w_dt == DT_BF16 && (dim & 7) == 0) {
-            const uint4* row = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(w_proj) + (size_t)i * dim);
-            for (int c = 0; c < dim >> 3; ++c) {
-                const uint4 v = row[c];
-                const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const float2 f = __bfloat1622float2(h2[k]);
-                    acc = fmaf(f.x, g[8 * c + 2 * k], acc);
-                    acc = fmaf(f.y, g[8 * c + 2 * k + 1], acc);
-                }
-            }
-        } else {
-            for (int j = 0; j < dim; ++j) acc = fmaf(ld_f(w_proj, (size_t)i * dim + j, w_dt), g[j], acc);
-        }
-        xs[i] = acc;                          // the thread's own place: nobody else reads the token's row any more
-        ss = fmaf(acc, acc, ss);
-    }
-    const float scale = alpha / sqrtf(block_sum(ss, scratch) * (1.0f / (float)width) + eps);
-    for (int i = threadIdx.x; i < width; i += blockDim.x)
-        x[(size_t)t * width + i] += (xs[i] * scale) * ld_f(w_norm, i, w_dt);
-}
-
-extern "C" int nncpu_token_side_step_fits(int width, int dim) {
-    return width > 0 && dim > 0 && (size_t)(width + dim) * 4 <= 48 * 1024;
-}
-
-extern "C" int nncpu_token_side_step(float* x, const void* w_gate, const void* w_proj, const void* w_norm, int w_dt,
-                                     const void* table, int table_dt, const int* ids, int ld, int col, int n_tok, int width,
-                                     int dim, float eps, float alpha, void* stream) {
-    NN_CHECK(n_tok >= 0 && nncpu_token_side_step_fits(width, dim) && col >= 0 && col + dim <= ld,
-             "token input: %d tokens of %d, lanes %d..%d of %d", n_tok, width, col, col + dim, ld);
-    if (n_tok == 0) return 0;
-    token_side_step_kernel<<<n_tok, 256, (size_t)(width + dim) * 4, (cudaStream_t)stream>>>(
-        x, w_gate, w_proj, w_norm, w_dt, table, table_dt, ids, ld, col, width, dim, eps, alpha);
-    NN_LAUNCH_OK("token input");
-    return 0;
-}
-
 extern "C" int nncpu_token_gate(const float* z, const void* table, int table_dt, const int* ids, int ld, int col,
                                 void* out, int out_dt, int n_tok, int dim, void* stream) {
     NN_CHECK(n_tok >= 0 && dim > 0 && col >= 0 && col + dim <= ld, "token gate: lanes %d..%d of %d", col, col + dim, ld);

@@ -208,25 +208,6 @@ def relu2(x, out, scale: float = 1.0) -> None:
     _call("generic", "nncpu_unary_act", _ptr(x), _ptr(out), _i(_code(out)), _l(x.numel()), _i(0), _f(scale), _stream())
 
 
-def token_side_step_fits(width: int, dim: int) -> bool:
-    """Whether ``token_side_step`` takes these sizes (a token's row and its gated lanes in one block's shared memory)."""
-    return width > 0 and dim > 0 and (width + dim) * 4 <= 48 * 1024
-
-
-def token_side_step(x, w_gate, w_proj, w_norm, table, ids, col: int, eps: float, alpha: float) -> None:
-    """x[t] += alpha * rmsnorm(W_proj (gelu_tanh(W_gate x[t]) * table[ids[t], col : col + dim])) * w_norm, for a step of
-    a few tokens in one launch; x float32, read as it is."""
-    n, width = x.shape
-    dim = w_gate.shape[0]
-    assert x.dtype == torch.float32 and x.is_contiguous() and w_gate.shape == (dim, width) and w_proj.shape == (width, dim)
-    assert w_gate.dtype == w_proj.dtype == w_norm.dtype and w_norm.numel() == width
-    assert w_gate.is_contiguous() and w_proj.is_contiguous()
-    assert table.dim() == 2 and table.is_contiguous() and ids.dtype == torch.int32 and ids.numel() >= n
-    _call("generic", "nncpu_token_side_step", _ptr(x), _ptr(w_gate), _ptr(w_proj), _ptr(w_norm), _i(_code(w_gate)),
-          _ptr(table), _i(_code(table)), _ptr(ids), _i(table.shape[1]), _i(col), _i(n), _i(width), _i(dim), _f(eps),
-          _f(alpha), _stream())
-
-
 def token_gate(z, table, ids, col: int, out) -> None:
     """out[t, j] = gelu_tanh(z[t, j]) * table[ids[t], col + j]: lanes of a per-token table gate a projection; z float32."""
     n, dim = z.shape

@@ -5,8 +5,7 @@ residual weight:
 
     g = gelu_tanh(W_gate x) * e,   y = W_proj g,   x <- x + m * y / sqrt(mean(y^2) + eps) * w
 
-The gate's product reads the stream itself, not a norm of it (rounded to the run's element type where a bfloat16 run
-multiplies on the tensor cores; a step of a few tokens does the whole part in one launch and reads the stream as it is).
+The gate's product reads the stream itself (rounded to the run's element type in a bfloat16 run), not a norm of it.
 The activation, the gating, the norm and the sum are 32-bit.  A layer that runs several times in a schedule uses the
 same lanes every time.
 """
@@ -17,9 +16,6 @@ import torch
 from ..kernels import ops
 from ..weights.params import ParamSpec
 from .base import Part
-
-
-FUSED_MAX_TOKENS = 16     # up to here a step's tokens each take one block that does the whole part
 
 
 class TokenSide(Part):
@@ -48,12 +44,6 @@ class TokenSide(Part):
     def forward(self, ctx, residual, mult: float) -> None:
         s, rt = self.spec, self.rt
         n = residual.shape[0]
-        if n <= FUSED_MAX_TOKENS and ops.token_side_step_fits(s.hidden_size, s.dim):
-            # a few tokens: both products, the gating and the norm in one launch (the stream is read as it is)
-            with rt.phase("side_step", nbytes=n * 2.0 * s.dim * s.hidden_size * self.w_gate.element_size(),
-                          flops=4.0 * n * s.dim * s.hidden_size):
-                ops.token_side_step(residual, self.w_gate, self.w_proj, self.w_norm, self.table, ctx.tok_ids, s.col, s.eps, mult)
-            return
         with rt.scope():
             if rt.dtype == torch.float32:
                 x = residual

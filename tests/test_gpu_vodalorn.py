@@ -392,21 +392,6 @@ def test_square_of_relu_in_the_products_and_alone(m):
     rt.check_status()
 
 
-@pytest.mark.parametrize("W,D,store", [(76, 5, torch.float32), (256, 32, torch.bfloat16), (2048, 128, torch.bfloat16),
-                                       (1000, 12, torch.bfloat16)])
-def test_a_tokens_own_input_in_one_launch(W, D, store):
-    g = np.random.RandomState(W)
-    n, V = 9, 50
-    x, table, ids = g.randn(n, W) * 2, g.randn(V, 3 * D), g.randint(0, V, size=n).tolist()
-    wt = {"s.gate": torch.tensor(g.randn(D, W) * 0.1).to(store), "s.proj": torch.tensor(g.randn(W, D) * 0.1).to(store),
-          "s.norm": torch.tensor(1 + 0.1 * g.randn(W)).to(store)}
-    w = {k: v.double().numpy() for k, v in wt.items()}
-    want = x + 0.7 * P.token_side(x, ids, w, "s", table[ids][:, D:2 * D], 1e-5)
-    xs = f32(x)
-    ops.token_side_step(xs, wt["s.gate"].to(DEV), wt["s.proj"].to(DEV), wt["s.norm"].to(DEV), f32(table), i32(ids), D, 1e-5, 0.7)
-    check(xs, want, 2e-5, "a token's own input")
-
-
 @pytest.mark.parametrize("W", [76, 2048, 4100, 9000])
 def test_what_joins_the_stream(W):
     """Two normed branches with a weight, one normed branch (the token's own input), a plain weighted sum, the lanes of
