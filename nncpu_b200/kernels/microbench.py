@@ -9,7 +9,7 @@ GFLOP/s for its row kernels and one attention block.
     python -m nncpu_b200.kernels.microbench attention-prefill BATCH TOKENS
     python -m nncpu_b200.kernels.microbench rmsnorm ROWS DIM
     python -m nncpu_b200.kernels.microbench gla BATCH TOKENS [--columns 2|4]
-    python -m nncpu_b200.kernels.microbench delta BATCH TOKENS [--lanes 4|8|16|32] [--columns 1|2]
+    python -m nncpu_b200.kernels.microbench delta BATCH TOKENS [--lanes 4|8|16|32] [--columns 1|2] [--channel-decay]
 
 Timing: the kernel is captured in a CUDA graph over enough different buffers
 that no launch finds its operands in L2, replayed, and timed with CUDA events.
@@ -234,10 +234,12 @@ def delta(args) -> None:
     slots = torch.arange(b, dtype=torch.int32, device=DEV)
     cu = torch.arange(0, n + 1, t, dtype=torch.int32, device=DEV)
     o = torch.empty(n, h * e, device=DEV)
-    ms = _time([lambda: ops.delta_scan(xc, gb, state, slots, cu, o, b, h, g, d, e)], args.once)
+    # --channel-decay: a decay per head and key channel (S <- diag(g) S) in place of one per head
+    chan = torch.rand(n, h * d, device=DEV) if args.channel_decay else None
+    ms = _time([lambda: ops.delta_scan(xc, gb, state, slots, cu, o, b, h, g, d, e, chan_g=chan)], args.once)
     ops.delta_scan_force()
-    nbytes = 4.0 * (n * (2 * d * g + e * h) + gb.numel() + o.numel()) + 8.0 * b * h * d * e
-    print(f"delta scan batch={b} tokens={t} heads={h} on {g} d={d} e={e}: {ms * 1e3:.1f} us, "
+    nbytes = 4.0 * (n * (2 * d * g + e * h) + gb.numel() + o.numel() + (0 if chan is None else chan.numel())) + 8.0 * b * h * d * e
+    print(f"delta scan{' (a decay per key channel)' if args.channel_decay else ''} batch={b} tokens={t} heads={h} on {g} d={d} e={e}: {ms * 1e3:.1f} us, "
           f"{3.0 * n * h * d * e / ms / 1e9:.2f} T multiply-adds/s, {nbytes / ms / 1e6:.0f} GB/s of inputs, outputs and state")
 
 
@@ -289,6 +291,7 @@ def main(argv=None) -> int:
     p.add_argument("--key-dim", type=int, default=128); p.add_argument("--value-dim", type=int, default=128)
     p.add_argument("--lanes", type=int, default=0, choices=[0, 4, 8, 16, 32], help="lanes a column of the state (0: by the layer's sizes)")
     p.add_argument("--columns", type=int, default=0, choices=[0, 1, 2], help="columns of the state a lane (0: by the layer's sizes)")
+    p.add_argument("--channel-decay", action="store_true", help="a decay per head and key channel instead of one per head")
     p.set_defaults(fn=delta)
     args = ap.parse_args(argv)
     if args.no_overlap:

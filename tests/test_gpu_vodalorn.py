@@ -85,8 +85,8 @@ CONFIGS = {
           "loop": {"start": 1, "stop": 3, "times": 2},
           "layers": [par(left(8, 2, 64, 64, 0.125, 100, rot(1e6, 64)), right(4, 64, 64, (0.9, 0.97, 0.99, 0.999), rot(1e4, 32)), mlp=dense(512)),
                      dlt(4, 4, 64, 64, 4, 16, 16, mlp=moe(8, 2, 64, 1.5, scale=2.0, groups=(4, 2))),
-                     par(left(4, 1, 128, 128, 0.09, 72, rot(5e5, 64)), right(2, 128, 128, (0.98, 0.995), rot(1e4, 128)), mlp=moe(16, 4, 128, 2.0)),
-                     dlt(2, 1, 128, 128, 2, 24, 8, mlp=dense(256)),
+                     par(left(4, 1, 128, 128, 0.09, 77, rot(4e5, 64)), right(2, 128, 128, (0.98, 0.995), rot(1e4, 128)), mlp=moe(16, 4, 128, 2.0)),
+                     dlt(2, 1, 128, 128, 2, 20, 8, mlp=dense(256)),
                      par(left(4, 4, 64, 128, 0.125, 64, rot(1e4, 32)), right(8, 32, 32, (0.9,) * 8, rot(1e6, 32)), mlp=dense(256))]},
     # values at the edges: a window of one key, 32 query heads on one key/value head, values of one lane, a decay of
     # zero, states of one row and of one column, a convolution of one tap, one expert, every expert chosen, every group
@@ -344,7 +344,7 @@ def test_channel_delta_remembers_a_write_far_back():
     assert np.abs(plain_channel_delta(other, z, conv_w, a_log, H, G, d, e)[-1] - want[-1]).max() > 1e-3 * np.abs(want[-1]).max()
 
 
-@pytest.mark.parametrize("E,top,groups,scale", [(8, 4, (4, 3), 2.0), (6, 2, (3, 2), 1.5), (16, 4, None, 1.0), (1, 1, None, 0.5),
+@pytest.mark.parametrize("E,top,groups,scale", [(8, 3, (4, 3), 2.5), (6, 2, (3, 2), 1.5), (16, 4, None, 1.0), (1, 1, None, 0.5),
                                                  (4, 4, (4, 4), 1.0), (12, 2, (6, 1), 3.0), (64, 8, (8, 2), 1.0)])
 def test_router_scores_over_all_experts_groups_and_scale(E, top, groups, scale):
     g = np.random.RandomState(E * 10 + top)
@@ -579,7 +579,7 @@ def test_unequal_batch_then_decoding_together_on_reused_slots(folders, name, dty
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_long_decoding_across_pages_and_windows(folders, dtype):
-    """420 decoded tokens after a prompt of 150: pages pass by and are given back, the windows (64, 72 and 100 keys) move
+    """420 decoded tokens after a prompt of 150: pages pass by and are given back, the windows (64, 77 and 100 keys) move
     over decoded tokens only, and the recurrent states have been rewritten 570 times."""
     cfg = CONFIGS["B"]
     n = 570
@@ -603,7 +603,7 @@ def test_long_prompt_on_the_tensor_core_paths(folders):
     float32 against the plain model."""
     cfg = CONFIGS["B"]
     t = toks(cfg, 610, 3)
-    rows = list(range(0, 600, 7)) + [63, 64, 71, 72, 73, 99, 100, 101, 127, 128, 129, 255, 256, 511, 512, 599]
+    rows = list(range(0, 600, 7)) + [63, 64, 76, 77, 78, 99, 100, 101, 127, 128, 129, 255, 256, 511, 512, 599]
     for dtype in ("bfloat16", "float32"):
         want = plain_logits(folders["B", dtype], t)
         model = Model.load(folders["B", dtype], dtype=dtype)
@@ -616,7 +616,7 @@ def test_long_prompt_on_the_tensor_core_paths(folders):
 
 
 @pytest.mark.parametrize("dim,vdim", [(16, 24), (64, 64)])
-@pytest.mark.parametrize("window", [1, 5, 64, 65, 72])
+@pytest.mark.parametrize("window", [1, 5, 64, 65, 77])
 def test_keys_just_inside_and_just_outside_a_window(tmp_path, window, dim, vdim):
     """One layer whose softmax side is so sharp that single keys take most of a row's weight: a key that is wrongly seen
     or missed at the window's edge changes the logits.  As a prompt across page borders, and token by token; with
@@ -763,7 +763,7 @@ def random_vodalorn(rs):
             count = int(rs.choice([c for c in (1, 2, 3, 4, 6) if E % c == 0]))
             keep = int(rs.randint(1, count + 1))
             top = int(rs.randint(1, keep * (E // count) + 1))
-            mlp = moe(E, top, int(rs.choice([16, 20, 64, 96])), float(rs.choice([0.8, 1.5, 7.0])),
+            mlp = moe(E, top, int(rs.choice([16, 20, 64, 80])), float(rs.choice([0.8, 1.25, 7.0])),
                       scale=float(rs.choice([1.0, 2.0, 2.5])), groups=(count, keep) if count > 1 or rs.rand() < 0.3 else None)
         else:
             mlp = None
@@ -771,24 +771,24 @@ def random_vodalorn(rs):
             kv, group, dim = int(rs.choice([1, 2, 3])), int(rs.choice([1, 2, 4, 8])), int(rs.choice([16, 24, 64, 128]))
             vdim = int(rs.choice([dim, dim, 8, 40, 128]))
             dims = int(rs.choice([dim, dim // 2, 2]))
-            window = None if rs.rand() < 0.15 else int(rs.choice([1, 3, 17, 64, 72, 100, 130]))
+            window = None if rs.rand() < 0.15 else int(rs.choice([1, 3, 17, 64, 77, 100, 130]))
             H, rd = int(rs.choice([1, 2, 3, 6])), int(rs.choice([8, 16, 32, 64]))
             rdims = int(rs.choice([rd, rd // 2]))
             layers.append(par(left(kv * group, kv, dim, vdim, float(rs.choice([dim ** -0.5, 0.2])), window,
-                                   rot(float(rs.choice([1e4, 5e5, 300.0])), dims) if rs.rand() < 0.9 else None),
+                                   rot(float(rs.choice([1e4, 4e5, 300.0])), dims) if rs.rand() < 0.9 else None),
                               right(H, rd, int(rs.choice([8, 32, 64])), [float(1 - 2.0 ** -(3 + j)) for j in range(H)],
                                     rot(float(rs.choice([1e4, 1e6])), rdims) if rs.rand() < 0.9 else None), mlp=mlp))
         else:
             kv, group = int(rs.choice([1, 2, 3])), int(rs.choice([1, 2, 3]))
             layers.append(dlt(kv * group, kv, int(rs.choice([8, 20, 64, 128])), int(rs.choice([8, 20, 64, 128])),
-                              int(rs.choice([1, 2, 4, 5])), int(rs.choice([3, 8, 24])), int(rs.choice([5, 8, 24])), mlp=mlp))
+                              int(rs.choice([1, 2, 4, 5])), int(rs.choice([3, 8, 20])), int(rs.choice([5, 8, 28])), mlp=mlp))
     cfg = {"architecture": "Vodalorn", "vocab": int(rs.randint(100, 600)), "width": width,
            "norm": {"eps": float(rs.choice([1e-6, 1e-5]))}, "residual_mult": float(rs.choice([1.0, 0.7, 0.5])), "layers": layers}
     if rs.rand() < 0.8:
-        cfg["embedding"] = {"bigram": {"buckets": int(rs.choice([17, 1021, 4093])), "mul_prev": int(rs.choice([1, 127, 99991])),
-                                       "mul_cur": int(rs.choice([1, 17, 31337]))}}
+        cfg["embedding"] = {"bigram": {"buckets": int(rs.choice([17, 1013, 4093])), "mul_prev": int(rs.choice([1, 131, 99991])),
+                                       "mul_cur": int(rs.choice([1, 23, 31337]))}}
     if rs.rand() < 0.8:
-        cfg["token_side"] = {"dim": int(rs.choice([1, 8, 24, 40]))}
+        cfg["token_side"] = {"dim": int(rs.choice([1, 8, 16, 40]))}
     if rs.rand() < 0.75:
         a = int(rs.randint(0, len(layers)))
         cfg["loop"] = {"start": a, "stop": int(rs.randint(a + 1, len(layers) + 1)), "times": int(rs.choice([1, 2, 3]))}
