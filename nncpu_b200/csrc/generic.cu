@@ -2531,11 +2531,14 @@ branch_norm_add_kernel(float* __restrict__ x, const float* __restrict__ a, const
 }
 
 // The common case, rows of a width that is a multiple of 4 and at most 256 * 4 * kVec: the branches' rows stay in
-// registers between the sums of squares and the scaling, so every row is read once.
+// registers between the sums of squares and the scaling, so every row is read once.  With ln_out the layer norm that
+// reads the stream next (weight ln_w, bias ln_b, ln_eps) is left there in the same pass: the new row is in registers.
 template <int kVec, bool kTwo>
 __global__ void __launch_bounds__(256)
 branch_norm_add_f32_kernel(float* __restrict__ x, const float* __restrict__ a, const void* __restrict__ wa,
-                           const float* __restrict__ b, const void* __restrict__ wb, int w_dt, float eps, float alpha, int dim) {
+                           const float* __restrict__ b, const void* __restrict__ wb, int w_dt, float eps, float alpha, int dim,
+                           const void* __restrict__ ln_w, const void* __restrict__ ln_b, int ln_dt, float ln_eps,
+                           void* __restrict__ ln_out, int ln_out_dt) {
     __shared__ float scratch[33];
     const size_t base = (size_t)blockIdx.x * dim;
     const int n4 = dim >> 2;
@@ -2572,19 +2575,59 @@ branch_norm_add_f32_kernel(float* __restrict__ x, const float* __restrict__ a, c
             o[e] = fmaf(alpha, v, o[e]);
         }
         reinterpret_cast<float4*>(x + base)[i] = make_float4(o[0], o[1], o[2], o[3]);
+        va[j] = make_float4(o[0], o[1], o[2], o[3]);        // the new row, for the norm that follows
+    }
+    if (ln_out == nullptr) return;
+    float s = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kVec; ++j)
+        if (threadIdx.x + j * 256 < n4) s += (va[j].x + va[j].y) + (va[j].z + va[j].w);
+    const float mean = block_sum(s, scratch) * (1.0f / (float)dim);
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) {
+        if (threadIdx.x + j * 256 >= n4) continue;
+        va[j].x -= mean; va[j].y -= mean; va[j].z -= mean; va[j].w -= mean;
+        ss = fmaf(va[j].x, va[j].x, ss); ss = fmaf(va[j].y, va[j].y, ss);
+        ss = fmaf(va[j].z, va[j].z, ss); ss = fmaf(va[j].w, va[j].w, ss);
+    }
+    const float scale = 1.0f / sqrtf(block_sum(ss, scratch) * (1.0f / (float)dim) + ln_eps);
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) {
+        const int i = threadIdx.x + j * 256;
+        if (i >= n4) continue;
+        float o[4] = {va[j].x * scale, va[j].y * scale, va[j].z * scale, va[j].w * scale};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            if (ln_w) o[e] *= ld_f(ln_w, 4 * i + e, ln_dt);
+            if (ln_b) o[e] += ld_f(ln_b, 4 * i + e, ln_dt);
+        }
+        const size_t at = base + 4 * i;
+        if (ln_out_dt == DT_BF16) {
+            __nv_bfloat162 h[2] = {__floats2bfloat162_rn(o[0], o[1]), __floats2bfloat162_rn(o[2], o[3])};
+            *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(ln_out) + at) = *reinterpret_cast<uint2*>(h);
+        } else {
+            *reinterpret_cast<float4*>(reinterpret_cast<float*>(ln_out) + at) = make_float4(o[0], o[1], o[2], o[3]);
+        }
     }
 }
 
+extern "C" int nncpu_branch_norm_add_takes_norm(int dim) { return dim > 0 && dim % 4 == 0 && dim <= 256 * 4 * 8; }
+
 extern "C" int nncpu_branch_norm_add(float* x, const float* a, const void* wa, const float* b, const void* wb, int w_dt,
-                                     float eps, float alpha, int n_tok, int dim, void* stream) {
+                                     float eps, float alpha, int n_tok, int dim, const void* ln_w, const void* ln_b,
+                                     int ln_dt, float ln_eps, void* ln_out, int ln_out_dt, void* stream) {
     NN_CHECK(n_tok >= 0 && dim > 0 && a != nullptr, "branch norm: %d rows of %d", n_tok, dim);
+    const bool vec = dim % 4 == 0 && dim <= 256 * 4 * 8 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)a % 16) == 0 &&
+                     ((uintptr_t)b % 16) == 0 && ((uintptr_t)ln_out % 16) == 0;
+    NN_CHECK(ln_out == nullptr || vec, "branch norm: a norm after rows of %d (a multiple of 4 up to 8192, 16-byte aligned)", dim);
     if (n_tok == 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
-    if (dim % 4 == 0 && dim <= 256 * 4 * 8 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)a % 16) == 0 && ((uintptr_t)b % 16) == 0) {
+    if (vec) {
 #define NN_BRANCH(V)                                                                                                  \
         do {                                                                                                          \
-            if (b) branch_norm_add_f32_kernel<V, true><<<n_tok, 256, 0, st>>>(x, a, wa, b, wb, w_dt, eps, alpha, dim);  \
-            else branch_norm_add_f32_kernel<V, false><<<n_tok, 256, 0, st>>>(x, a, wa, b, wb, w_dt, eps, alpha, dim);   \
+            if (b) branch_norm_add_f32_kernel<V, true><<<n_tok, 256, 0, st>>>(x, a, wa, b, wb, w_dt, eps, alpha, dim, ln_w, ln_b, ln_dt, ln_eps, ln_out, ln_out_dt);  \
+            else branch_norm_add_f32_kernel<V, false><<<n_tok, 256, 0, st>>>(x, a, wa, b, wb, w_dt, eps, alpha, dim, ln_w, ln_b, ln_dt, ln_eps, ln_out, ln_out_dt);   \
         } while (0)
         if (dim <= 1024) NN_BRANCH(1);
         else if (dim <= 2048) NN_BRANCH(2);

@@ -189,17 +189,30 @@ def stream_axpy(x, y, alpha: float) -> None:
     _call("generic", "nncpu_stream_axpy", _ptr(x), _ptr(y), _f(alpha), _l(x.numel()), _stream())
 
 
-def branch_norm_add(x, a, wa, b, wb, eps: float, alpha: float) -> None:
+def branch_norm_add_takes_norm(dim: int) -> bool:
+    """Whether ``branch_norm_add`` can leave the layer norm that follows (``then_norm``) for rows of ``dim`` lanes."""
+    return dim > 0 and dim % 4 == 0 and dim <= 8192
+
+
+def branch_norm_add(x, a, wa, b, wb, eps: float, alpha: float, then_norm=None) -> None:
     """x += alpha * (rmsnorm(a) * wa + rmsnorm(b) * wb) row by row (``b`` None: the first term alone; a weight None:
-    ones); x, a, b float32."""
+    ones); x, a, b float32.  ``then_norm`` = (weight, bias, eps, out): the layer norm of the new rows is left in ``out``
+    in the same pass (where ``branch_norm_add_takes_norm`` says so)."""
     n, dim = x.shape
+    ln_w = ln_b = ln_out = None
+    ln_eps = 0.0
+    if then_norm is not None:
+        ln_w, ln_b, ln_eps, ln_out = then_norm
+        assert branch_norm_add_takes_norm(dim) and ln_out.shape == x.shape and ln_out.is_contiguous()
+        assert ln_w.numel() == ln_b.numel() == dim and ln_w.dtype == ln_b.dtype
     assert x.dtype == a.dtype == torch.float32 and a.shape == x.shape and x.is_contiguous() and a.is_contiguous()
     assert b is None or (b.dtype == torch.float32 and b.shape == x.shape and b.is_contiguous())
     assert wa is None or wa.numel() == dim
     assert wb is None or (wb.numel() == dim and (wa is None or wa.dtype == wb.dtype))
     w = wa if wa is not None else wb
     _call("generic", "nncpu_branch_norm_add", _ptr(x), _ptr(a), _ptr(wa), _ptr(b), _ptr(wb), _i(_code(w)), _f(eps),
-          _f(alpha), _i(n), _i(dim), _stream())
+          _f(alpha), _i(n), _i(dim), _ptr(ln_w), _ptr(ln_b), _i(_code(ln_w)), _f(ln_eps), _ptr(ln_out), _i(_code(ln_out)),
+          _stream())
 
 
 def relu2(x, out, scale: float = 1.0) -> None:

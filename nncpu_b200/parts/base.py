@@ -104,6 +104,18 @@ class DeferredNorm:
         return self.request.norm.forward(ctx, self.request.residual)
 
 
+def norm_output_buffer(ctx, rt, shape) -> torch.Tensor:
+    """Where a part that closes a sublayer leaves the output of the norm that reads the stream next (a request with
+    ``wants_output``): two buffers of the step take turns, so that one can be written while the other is still read."""
+    turn = ctx.memo.get("norm_out_turn", 0)
+    ctx.memo["norm_out_turn"] = 1 - turn
+    key = ("norm_out", turn, tuple(shape))
+    buf = ctx.memo.get(key)
+    if buf is None:
+        buf = ctx.memo[key] = rt.empty(*shape, keep=True)
+    return buf
+
+
 class PositionEncoding(Part):
     """``tables(ctx)`` gives float32 [n_tokens, half, 2]: for every token of the
     step the (cos, sin) that rotate the pairs (i, i + half) of a head's first

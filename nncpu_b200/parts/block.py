@@ -54,12 +54,25 @@ class PreNormBlock(Block):
         return [(self.mixer.kv_request(), self.mixer.state_request())]
 
     def entry_norm_request(self, ctx, residual):
-        return self.norm1.request(ctx, residual) if self.mixer.accepts_deferred_norm else None
+        req = self.norm1.request(ctx, residual)
+        if req is not None and req.wants_output:     # a finished output: whatever the mixer is, it can read it
+            return req
+        return req if self.mixer.accepts_deferred_norm else None
+
+    @staticmethod
+    def _finished(norm, ctx, residual, request):
+        """``norm``'s output: what the part that wrote the stream last left, if it fulfilled this very norm's request for
+        a finished output; else the norm's own kernel."""
+        if request is not None and request.norm is norm and request.output is not None:
+            return request.output
+        return norm.forward(ctx, residual)
 
     @staticmethod
     def _normed(norm, consumer, ctx, residual, request):
         """``norm``'s output for ``consumer``: what the writer of the residual left, if it fulfilled the request
         of this very norm and the consumer takes it unfinished; else the norm's own kernel."""
+        if request is not None and request.norm is norm and request.output is not None:
+            return request.output           # finished, by a kernel that closed the sublayer before
         if (request is not None and request.norm is norm and request.result is not None
                 and consumer.accepts_deferred_norm):
             return request.result
@@ -92,21 +105,30 @@ class PreNormBlock(Block):
         ff = self.feed_forward
         if self.mult != 1.0 or self.side is not None:
             # the sublayers' products are not the last writes into the stream: no norm rides on them
+            # (a mixer that closes with a kernel of its own, and the side part, can leave the norm that follows them)
+            asked = None
             with self.rt.scope():
-                x = self.norm1.forward(ctx, residual)
+                x = self._finished(self.norm1, ctx, residual, handed)
+                if ff is not None and getattr(self.mixer, "closes_stream", False):
+                    asked = self.norm2.request(ctx, residual)
+                    if asked is not None and not asked.wants_output:
+                        asked = None
+                ctx.next_norm = asked
                 if self.mult != 1.0:
                     self._scaled(ctx, self.mixer, residual, lambda out: self.mixer.forward(ctx, x, out, caches[0]))
                 else:
                     self.mixer.forward(ctx, x, residual, caches[0])
+                ctx.next_norm = None
             if ff is not None:
                 with self.rt.scope():
-                    x = self.norm2.forward(ctx, residual)
+                    x = self._finished(self.norm2, ctx, residual, asked)
                     if self.mult != 1.0:
                         self._scaled(ctx, ff, residual, lambda out: ff.forward(ctx, x, out))
                     else:
                         ff.forward(ctx, x, residual)
             if self.side is not None:
-                self.side.forward(ctx, residual, self.mult)
+                self.side.forward(ctx, residual, self.mult, then=after)
+            ctx.next_norm = after       # the block that follows finds its request there, fulfilled or not
             return
         with self.rt.scope():       # the mixer's temporaries are done with when the feed-forward starts
             x = self._normed(self.norm1, self.mixer, ctx, residual, handed)

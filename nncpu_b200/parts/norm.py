@@ -72,3 +72,14 @@ class LayerNorm(Norm):
         with self.rt.phase("norm"):
             ops.layernorm(residual, self.gamma, self.beta, self.eps, out, rows)
         return out
+
+    def request(self, ctx, residual):
+        """A kernel that closes a sublayer with a norm of its own (``ops.branch_norm_add``) holds the stream's new rows in
+        registers and can leave this norm's output in the same pass: the request asks for that (``wants_output``)."""
+        if residual.dtype != torch.float32 or not ops.branch_norm_add_takes_norm(self.size):
+            return None
+        return NormRequest(self, residual, self.gamma, self.eps, self.size, wants_output=True)
+
+    def closing(self, out):
+        """What ``ops.branch_norm_add`` takes as ``then_norm`` to leave this norm's output in ``out``."""
+        return (self.gamma, self.beta, self.eps, out)

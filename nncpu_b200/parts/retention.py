@@ -106,6 +106,7 @@ class Retention(Mixer):
 @register_mixer("mixer_pair")
 class MixerPair(Mixer):
     scales_output = True        # what it adds to the stream is multiplied by ctx.out_scale
+    closes_stream = True        # its last kernel holds the stream's new rows: it can leave the layer norm that follows
 
     def __init__(self, spec, reads_other_cache: bool = False):
         self.spec = spec
@@ -145,6 +146,7 @@ class MixerPair(Mixer):
         if getattr(ctx, "branch_is_fresh", False):
             raise UnsupportedModel(f"{s.name}: a pair of mixers adds into the stream it is given")
         scale = float(getattr(ctx, "out_scale", 1.0))
+        then = getattr(ctx, "next_norm", None)
         a = rt.empty(*residual.shape, dtype=torch.float32)
         b = rt.empty(*residual.shape, dtype=torch.float32)
         ctx.next_norm = None                # neither mixer's last product is the last write into the stream
@@ -157,4 +159,10 @@ class MixerPair(Mixer):
         finally:
             ctx.branch_is_fresh, ctx.out_scale = False, scale
         with rt.phase("norm", nbytes=16.0 * residual.numel()):
-            ops.branch_norm_add(residual, a, self.w_left, b, self.w_right, s.eps, scale * s.weight)
+            if then is not None and then.wants_output and hasattr(then.norm, "closing") and then.residual is residual:
+                out = base.norm_output_buffer(ctx, rt, residual.shape)
+                ops.branch_norm_add(residual, a, self.w_left, b, self.w_right, s.eps, scale * s.weight,
+                                    then_norm=then.norm.closing(out))
+                then.output = out
+            else:
+                ops.branch_norm_add(residual, a, self.w_left, b, self.w_right, s.eps, scale * s.weight)

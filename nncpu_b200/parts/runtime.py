@@ -174,7 +174,7 @@ class Runtime:
             norm_in = None
         if takes:
             norm_out = None
-            if (fuses and then_norm is not None and self._norm_bins is not None and epilogue == "plain"
+            if (fuses and then_norm is not None and not then_norm.wants_output and self._norm_bins is not None and epilogue == "plain"
                     and out.dtype == torch.float32 and out.shape[1] == then_norm.size == w.shape[0] and out.is_contiguous()
                     and self._norm_bins.shape[1] == (ops.SKINNY_MAX_TOKENS if few else out.shape[0])):
                 # two sets of accumulators (and of rows times gamma) take turns: this product adds into one (zero

@@ -15,7 +15,7 @@ import torch
 
 from ..kernels import ops
 from ..weights.params import ParamSpec
-from .base import Part
+from .base import Part, norm_output_buffer
 
 
 class TokenSide(Part):
@@ -41,7 +41,8 @@ class TokenSide(Part):
     def weight_bytes(self):
         return sum(t.numel() * t.element_size() for t in (self.w_gate, self.w_proj))
 
-    def forward(self, ctx, residual, mult: float) -> None:
+    def forward(self, ctx, residual, mult: float, then=None) -> None:
+        """``then``: the request of the norm that reads the stream next; the closing kernel can leave its output."""
         s, rt = self.spec, self.rt
         n = residual.shape[0]
         with rt.scope():
@@ -61,4 +62,9 @@ class TokenSide(Part):
             with rt.phase("side_proj", self.w_proj, n):
                 rt.linear(g, self.w_proj, None, y)
             with rt.phase("norm", nbytes=12.0 * y.numel()):
-                ops.branch_norm_add(residual, y, self.w_norm, None, None, s.eps, mult)
+                if then is not None and then.wants_output and hasattr(then.norm, "closing") and then.residual is residual:
+                    out = norm_output_buffer(ctx, rt, residual.shape)
+                    ops.branch_norm_add(residual, y, self.w_norm, None, None, s.eps, mult, then_norm=then.norm.closing(out))
+                    then.output = out
+                else:
+                    ops.branch_norm_add(residual, y, self.w_norm, None, None, s.eps, mult)
