@@ -645,6 +645,53 @@ def test_keys_just_inside_and_just_outside_a_window(tmp_path, window, dim, vdim)
         close(out, want[3:140], dtype, f"window {window}: decoded from the start")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_twenty_requests_decode_together(folders, dtype):
+    """More sequences than the few-token products take (20 prompts of 1 to 150 tokens in one step, then 6 decode steps of 20
+    tokens through the captured step of 32 rows, 12 of them padding) against each request alone in the plain model."""
+    cfg = CONFIGS["B"]
+    lens = [1 + (37 * i) % 150 for i in range(20)]
+    seqs = [toks(cfg, n + 6, 200 + i) for i, n in enumerate(lens)]
+    want = [plain_logits(folders["B", dtype], t) for t in seqs]
+    model = Model.load(folders["B", dtype], dtype=dtype)
+    engine = Engine(model, max_tokens=64 * 64)
+    slots = [engine.alloc_slot() for _ in seqs]
+    rows = Rows(dtype, "twenty requests")
+    out = engine.step(slots, [t[:n] for t, n in zip(seqs, lens)], [[n - 1] for n in lens])
+    for b in range(20):
+        rows.add(out[b], want[b][lens[b] - 1], f"prompt {b}")
+    for step in range(6):
+        out = engine.step(slots, [[seqs[b][lens[b] + step]] for b in range(20)])
+        for b in range(20):
+            rows.add(out[b], want[b][lens[b] + step], f"request {b} decoded token {step}")
+    rows.done()
+    engine.cache.check()
+    model.rt.check_status()
+
+
+@pytest.mark.parametrize("dim", [64, 128])
+def test_many_query_heads_on_one_key_value_head_at_tensor_core_sizes(tmp_path, dim):
+    """32 query heads on one key/value head with heads of 64 and 128 lanes, a partly rotated head, a window that ends inside
+    a page: a prompt across pages and token by token, in both run types."""
+    cfg = {"architecture": "Vodalorn", "vocab": 120, "width": 128, "norm": {"eps": 1e-5}, "residual_mult": 0.8,
+           "layers": [par(left(32, 1, dim, dim, dim ** -0.5, 50, rot(1e4, dim // 2)), right(2, 16, 16, (0.9, 0.99), rot(1e4, 16)), mlp=dense(64)),
+                      par(left(20, 1, dim, dim, dim ** -0.5, None, rot(1e4, dim)), right(1, 32, 8, (0.95,)), mlp=None)]}
+    t = toks(cfg, 150, 6)
+    for dtype in DTYPES:
+        folder = write_folder(tmp_path / dtype, cfg, 9, STORE[dtype], sharpen=3.0)
+        want = plain_logits(folder, t)
+        model = Model.load(folder, dtype=dtype)
+        engine = Engine(model, max_tokens=512)
+        s = engine.alloc_slot()
+        close(engine.step([s], [t[:130]], [list(range(130))]), want[:130], dtype, f"{dtype}: a prompt")
+        out = torch.cat([engine.step([s], [[t[i]]]).clone() for i in range(130, 150)])
+        close(out, want[130:], dtype, f"{dtype}: decoded after it")
+        s2 = engine.alloc_slot()
+        out = torch.cat([engine.step([s2], [t[i:i + 3]], [[0, 1, 2]]).clone() for i in range(0, 150, 3)])
+        close(out, want, dtype, f"{dtype}: portions of three tokens")
+        model.rt.check_status()
+
+
 def test_a_key_far_back(tmp_path):
     """Attention without a window, sharp queries and keys, 560 positions: most rows look far back and across pages."""
     cfg = {"architecture": "Vodalorn", "vocab": 64, "width": 48, "norm": {"eps": 1e-5},
