@@ -221,6 +221,22 @@ def relu2(x, out, scale: float = 1.0) -> None:
     _call("generic", "nncpu_unary_act", _ptr(x), _ptr(out), _i(_code(out)), _l(x.numel()), _i(0), _f(scale), _stream())
 
 
+GATE_ROWS_MAX_TOKENS = 16
+
+
+def token_gate_rows(x, w, table, ids, col: int, out) -> None:
+    """out[t, j] = gelu_tanh(w[j] . x[t]) * table[ids[t], col + j] for a step of up to ``GATE_ROWS_MAX_TOKENS`` tokens
+    in one launch: the product, the activation and the gating.  x float32 [n, width] (read as it is), w [dim, width]."""
+    n, width = x.shape
+    dim = w.shape[0]
+    assert n <= GATE_ROWS_MAX_TOKENS and x.dtype == torch.float32 and x.is_contiguous()
+    assert w.shape == (dim, width) and w.is_contiguous() and out.shape == (n, dim) and out.is_contiguous()
+    assert table.dim() == 2 and table.is_contiguous() and 0 <= col and col + dim <= table.shape[1]
+    assert ids.dtype == torch.int32 and ids.numel() >= n
+    _call("generic", "nncpu_token_gate_rows", _ptr(x), _ptr(w), _i(_code(w)), _ptr(table), _i(_code(table)), _ptr(ids),
+          _i(table.shape[1]), _i(col), _ptr(out), _i(_code(out)), _i(n), _i(width), _i(dim), _stream())
+
+
 def token_gate(z, table, ids, col: int, out) -> None:
     """out[t, j] = gelu_tanh(z[t, j]) * table[ids[t], col + j]: lanes of a per-token table gate a projection; z float32."""
     n, dim = z.shape

@@ -5,7 +5,9 @@ residual weight:
 
     g = gelu_tanh(W_gate x) * e,   y = W_proj g,   x <- x + m * y / sqrt(mean(y^2) + eps) * w
 
-The gate's product reads the stream itself (rounded to the run's element type in a bfloat16 run), not a norm of it.
+The gate's product reads the stream itself, not a norm of it: rounded to the run's element type where a bfloat16 run
+multiplies on the tensor cores, and as it is in a step of a few tokens, whose gate is one launch (product, activation,
+gating).
 The activation, the gating, the norm and the sum are 32-bit.  A layer that runs several times in a schedule uses the
 same lanes every time.
 """
@@ -46,18 +48,24 @@ class TokenSide(Part):
         s, rt = self.spec, self.rt
         n = residual.shape[0]
         with rt.scope():
-            if rt.dtype == torch.float32:
-                x = residual
-            else:
-                x = rt.empty(n, s.hidden_size)
-                with rt.phase("side_gate"):
-                    ops.concat_rows(residual, None, x)
-            z = rt.empty(n, s.dim, dtype=torch.float32)
-            with rt.phase("side_gate", self.w_gate, n):
-                rt.linear(x, self.w_gate, None, z)
             g = rt.empty(n, s.dim)
-            with rt.phase("side_gate"):
-                ops.token_gate(z, self.table, ctx.tok_ids, s.col, g)
+            if n <= ops.GATE_ROWS_MAX_TOKENS:
+                # a few tokens: the gate's product, the activation and the gating in one launch (a warp a row of the
+                # matrix, which is read once for all tokens; the stream is read as it is)
+                with rt.phase("side_gate", self.w_gate, n):
+                    ops.token_gate_rows(residual, self.w_gate, self.table, ctx.tok_ids, s.col, g)
+            else:
+                if rt.dtype == torch.float32:
+                    x = residual
+                else:
+                    x = rt.empty(n, s.hidden_size)
+                    with rt.phase("side_gate"):
+                        ops.concat_rows(residual, None, x)
+                z = rt.empty(n, s.dim, dtype=torch.float32)
+                with rt.phase("side_gate", self.w_gate, n):
+                    rt.linear(x, self.w_gate, None, z)
+                with rt.phase("side_gate"):
+                    ops.token_gate(z, self.table, ctx.tok_ids, s.col, g)
             y = rt.empty(n, s.hidden_size, dtype=torch.float32)
             with rt.phase("side_proj", self.w_proj, n):
                 rt.linear(g, self.w_proj, None, y)

@@ -392,6 +392,20 @@ def test_square_of_relu_in_the_products_and_alone(m):
     rt.check_status()
 
 
+@pytest.mark.parametrize("W,D,store", [(76, 5, torch.float32), (256, 32, torch.bfloat16), (2048, 128, torch.bfloat16),
+                                       (1000, 12, torch.bfloat16), (4096, 256, torch.float32)])
+def test_the_gate_of_a_tokens_own_input_for_a_few_tokens(W, D, store):
+    g = np.random.RandomState(W)
+    for n in (1, 9, 16):
+        V = 50
+        x, table, ids = g.randn(n, W) * 2, g.randn(V, 3 * D), g.randint(0, V, size=n).tolist()
+        w = torch.tensor(g.randn(D, W) * 0.1).to(store)
+        want = P.gelu_tanh(x @ w.double().numpy().T) * table[ids][:, D:2 * D]
+        out = torch.empty(n, D, dtype=torch.float32, device=DEV)
+        ops.token_gate_rows(f32(x), w.to(DEV), f32(table), i32(ids), D, out)
+        check(out, want, 2e-5, f"{n} tokens")
+
+
 @pytest.mark.parametrize("W", [76, 2048, 4100, 9000])
 def test_what_joins_the_stream(W):
     """Two normed branches with a weight, one normed branch (the token's own input), a plain weighted sum, the lanes of
