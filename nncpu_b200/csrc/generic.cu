@@ -2675,63 +2675,54 @@ __global__ void token_gate_kernel(const float* __restrict__ z, const void* __res
 }
 
 // The same for a step of a few tokens, with the product in front of it: out[t, j] = gelu_tanh(W[j] . x[t]) *
-// table[ids[t], col + j].  A warp owns one row j of W [dim, width] and walks it once for all the step's tokens (up to
-// kGateRowsMaxTokens), so the matrix is read once; x float32 [n_tok, width] is read as it is (not rounded).
+// table[ids[t], col + j].  A warp owns one (row j of W [dim, width], token t) pair and asks for its whole share of the
+// row and of the token before it multiplies (a chain of dependent loads from memory is what such a small product would
+// otherwise wait for); a row is read from memory once and by the other tokens' warps from L2.  x float32
+// [n_tok, width] is read as it is (not rounded).
 constexpr int kGateRowsMaxTokens = 16;
+constexpr int kGateRowsChunk = 8;          // 16-byte pieces of a row that a lane has in flight
 
 __global__ void __launch_bounds__(256)
 token_gate_rows_kernel(const float* __restrict__ x, const void* __restrict__ w, int w_dt, const void* __restrict__ table,
                        int table_dt, const int* __restrict__ ids, int ld, int col, void* __restrict__ out, int out_dt,
-                       int n_tok, int width, int dim) {
+                       int width, int dim) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int j = blockIdx.x * 8 + warp;
+    const int j = blockIdx.x * 8 + warp, t = blockIdx.y;
     if (j >= dim) return;
-    float acc[kGateRowsMaxTokens];
-#pragma unroll
-    for (int t = 0; t < kGateRowsMaxTokens; ++t) acc[t] = 0.0f;
+    float s = 0.0f;
     if (w_dt == DT_BF16 && (width & 7) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 &&
         (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
         const uint4* row = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(w) + (size_t)j * width);
-        for (int c = lane; c < (width >> 3); c += 32) {
-            const uint4 v = row[c];
-            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&v);
-            float wf[8];
+        const float4* xr = reinterpret_cast<const float4*>(x + (size_t)t * width);
+        const int n8 = width >> 3;
+        for (int c0 = 0; c0 < n8; c0 += 32 * kGateRowsChunk) {
+            uint4 wv[kGateRowsChunk];
+            float4 xa[kGateRowsChunk], xb[kGateRowsChunk];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const float2 f = __bfloat1622float2(h2[k]);
-                wf[2 * k] = f.x;
-                wf[2 * k + 1] = f.y;
+            for (int k = 0; k < kGateRowsChunk; ++k) {
+                const int c = c0 + lane + 32 * k;
+                const bool in = c < n8;
+                wv[k] = in ? row[c] : make_uint4(0, 0, 0, 0);
+                xa[k] = in ? xr[2 * c] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                xb[k] = in ? xr[2 * c + 1] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             }
 #pragma unroll
-            for (int t = 0; t < kGateRowsMaxTokens; ++t) {
-                if (t >= n_tok) break;
-                const float4* xp = reinterpret_cast<const float4*>(x + (size_t)t * width + 8 * c);
-                const float4 a = xp[0], b = xp[1];
-                float s = acc[t];
-                s = fmaf(wf[0], a.x, s); s = fmaf(wf[1], a.y, s); s = fmaf(wf[2], a.z, s); s = fmaf(wf[3], a.w, s);
-                s = fmaf(wf[4], b.x, s); s = fmaf(wf[5], b.y, s); s = fmaf(wf[6], b.z, s); s = fmaf(wf[7], b.w, s);
-                acc[t] = s;
+            for (int k = 0; k < kGateRowsChunk; ++k) {
+                const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&wv[k]);
+                const float2 f0 = __bfloat1622float2(h2[0]), f1 = __bfloat1622float2(h2[1]);
+                const float2 f2 = __bfloat1622float2(h2[2]), f3 = __bfloat1622float2(h2[3]);
+                s = fmaf(f0.x, xa[k].x, s); s = fmaf(f0.y, xa[k].y, s); s = fmaf(f1.x, xa[k].z, s); s = fmaf(f1.y, xa[k].w, s);
+                s = fmaf(f2.x, xb[k].x, s); s = fmaf(f2.y, xb[k].y, s); s = fmaf(f3.x, xb[k].z, s); s = fmaf(f3.y, xb[k].w, s);
             }
         }
     } else {
-        for (int i = lane; i < width; i += 32) {
-            const float wv = ld_f(w, (size_t)j * width + i, w_dt);
-#pragma unroll
-            for (int t = 0; t < kGateRowsMaxTokens; ++t) {
-                if (t >= n_tok) break;
-                acc[t] = fmaf(wv, x[(size_t)t * width + i], acc[t]);
-            }
-        }
+        for (int i = lane; i < width; i += 32) s = fmaf(ld_f(w, (size_t)j * width + i, w_dt), x[(size_t)t * width + i], s);
     }
-#pragma unroll
-    for (int t = 0; t < kGateRowsMaxTokens; ++t) {
-        if (t >= n_tok) break;
-        const float z = warp_sum(acc[t]);
-        if (lane == 0) {
-            const int id = ids[t];
-            const float e = id >= 0 ? ld_f(table, (size_t)id * ld + col + j, table_dt) : 0.0f;
-            st_f(out, (size_t)t * dim + j, out_dt, gelu_tanh_f(z) * e);
-        }
+    const float z = warp_sum(s);
+    if (lane == 0) {
+        const int id = ids[t];
+        const float e = id >= 0 ? ld_f(table, (size_t)id * ld + col + j, table_dt) : 0.0f;
+        st_f(out, (size_t)t * dim + j, out_dt, gelu_tanh_f(z) * e);
     }
 }
 
@@ -2742,8 +2733,8 @@ extern "C" int nncpu_token_gate_rows(const float* x, const void* w, int w_dt, co
              "token gate (few tokens): %d tokens (at most %d) of %d, lanes %d..%d of %d", n_tok, kGateRowsMaxTokens, width,
              col, col + dim, ld);
     if (n_tok == 0) return 0;
-    token_gate_rows_kernel<<<(dim + 7) / 8, 256, 0, (cudaStream_t)stream>>>(x, w, w_dt, table, table_dt, ids, ld, col, out,
-                                                                           out_dt, n_tok, width, dim);
+    token_gate_rows_kernel<<<dim3((dim + 7) / 8, n_tok), 256, 0, (cudaStream_t)stream>>>(x, w, w_dt, table, table_dt, ids, ld,
+                                                                                        col, out, out_dt, width, dim);
     NN_LAUNCH_OK("token gate (few tokens)");
     return 0;
 }
