@@ -414,7 +414,7 @@ def vodalorn_configs(z: dict):
                           "conv": z["conv"], "rank": z["rank"], "gate_rank": z["rank"]}}
 
     vod = config_from_dict({"architecture": "Vodalorn", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
-                            "residual_mult": 0.7, "token_side": {"dim": z["side"]},
+                            "residual_mult": 0.8, "token_side": {"dim": z["side"]},
                             "embedding": {"bigram": {"buckets": z["buckets"], "mul_prev": 8191, "mul_cur": 31}},
                             "loop": {"start": 1, "stop": 4, "times": 2},
                             "layers": [pair(dense), delta(moe), pair(moe), pair(moe), delta(dense)]})

@@ -80,11 +80,11 @@ CONFIGS = {
                      dlt(3, 3, 10, 36, 2, 4, 9, mlp=dense(40))]},
     # sizes the tensor-core paths take: heads of 64 and 128 lanes with values of the same size (and one layer with
     # values of another size), whole and partly rotated heads, states of 64 x 64 and 128 x 128, experts of 64 and 128
-    "B": {"architecture": "Vodalorn", "vocab": 640, "width": 256, "norm": {"eps": 1e-5}, "residual_mult": 0.7,
+    "B": {"architecture": "Vodalorn", "vocab": 640, "width": 256, "norm": {"eps": 1e-5}, "residual_mult": 0.75,
           "embedding": {"bigram": {"buckets": 509, "mul_prev": 1009, "mul_cur": 13}}, "token_side": {"dim": 32},
           "loop": {"start": 1, "stop": 3, "times": 2},
           "layers": [par(left(8, 2, 64, 64, 0.125, 100, rot(1e6, 64)), right(4, 64, 64, (0.9, 0.97, 0.99, 0.999), rot(1e4, 32)), mlp=dense(512)),
-                     dlt(4, 4, 64, 64, 4, 16, 16, mlp=moe(8, 2, 64, 1.5, scale=2.0, groups=(4, 2))),
+                     dlt(4, 4, 64, 64, 4, 16, 16, mlp=moe(8, 2, 64, 1.25, scale=1.75, groups=(4, 2))),
                      par(left(4, 1, 128, 128, 0.09, 77, rot(4e5, 64)), right(2, 128, 128, (0.98, 0.995), rot(1e4, 128)), mlp=moe(16, 4, 128, 2.0)),
                      dlt(2, 1, 128, 128, 2, 20, 8, mlp=dense(256)),
                      par(left(4, 4, 64, 128, 0.125, 64, rot(1e4, 32)), right(8, 32, 32, (0.9,) * 8, rot(1e6, 32)), mlp=dense(256))]},
